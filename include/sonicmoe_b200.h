@@ -1,0 +1,102 @@
+/* C ABI of libsonicmoe_b200.so: the sm_100a kernels behind the `sonicmoe` MoE layer.
+ *
+ * Conventions
+ *   - every pointer is a device pointer unless said otherwise; the caller owns all buffers, the
+ *     library borrows them for the duration of the stream-ordered launch and allocates nothing;
+ *   - `stream` is a cudaStream_t passed as void*;
+ *   - functions return SMOE_OK (0) or a negative SMOE_ERR_* code; a non-zero return means nothing
+ *     was launched; nothing throws;
+ *   - bf16 tensors are row-major and 16-byte aligned; index tensors are int32;
+ *   - T tokens, H hidden size, I expert intermediate size, E experts, K experts per token,
+ *     TK routed (token, expert) pairs; "grouped" rows are sorted by expert: expert e owns rows
+ *     [expert_offset[e], expert_offset[e+1]);
+ *   - `status` (optional, may be NULL) is a device int32 the GEMM kernels set to a non-zero
+ *     SMOE_ST_* code when one of their bounded waits ran out; the caller zeroes it and reads it.
+ *
+ * Each entry point cites the operator of the reference (path within the sonic-moe project) that it
+ * stands in for.
+ */
+#ifndef SONICMOE_B200_H_
+#define SONICMOE_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+  SMOE_OK = 0,
+  SMOE_ERR_SHAPE = -1,     /* unsupported or inconsistent sizes */
+  SMOE_ERR_ALIGNMENT = -2, /* a pointer or pitch is not 16-byte aligned */
+  SMOE_ERR_DRIVER = -3,    /* no usable CUDA driver / device */
+  SMOE_ERR_TENSORMAP = -4, /* the driver rejected a TMA descriptor */
+  SMOE_ERR_LAUNCH = -5,    /* the kernel launch itself failed */
+  SMOE_ERR_DTYPE = -6,     /* unknown dtype code */
+  SMOE_ERR_WORKSPACE = -7  /* workspace missing or too small */
+};
+
+enum { SMOE_ST_OK = 0, SMOE_ST_TIMEOUT_PRODUCER = 1, SMOE_ST_TIMEOUT_MMA = 2, SMOE_ST_TIMEOUT_EPILOGUE = 3 };
+
+/* dtype codes for tensors whose type the caller chooses */
+enum { SMOE_F32 = 0, SMOE_BF16 = 1, SMOE_I32 = 2, SMOE_I64 = 3 };
+
+/* Library version, for the loader to check that it found the right build. */
+int smoe_abi_version(void);
+
+/* ---------------------------------------------------------------------------------------------
+ * Grouped GEMMs (tcgen05 / TMEM / TMA)
+ * ------------------------------------------------------------------------------------------- */
+
+/* z[r, :] = x[x_gather_idx[r], :] @ W1[e]^T, y1[r, j] = silu(z[r, 2j]) * z[r, 2j+1] for every grouped
+ * row r of expert e.  x (T,H); w1 (E,2I,H) gate/up rows interleaved; z (TK,2I) or NULL (inference);
+ * y1 (TK,I).  Replaces sonicmoe::_up_projection_forward (sonicmoe/functional/forward.py:53-126). */
+int smoe_up_projection_forward(const void* x, const void* w1, void* z, void* y1, const int* expert_offset,
+                               const int* x_gather_idx, int T, int H, int I, int E, int TK, int* status,
+                               void* stream);
+
+/* y2[r, :] = y1[r, :] @ W2[e]^T.  w2 (E,H,I); y2 (TK,H).
+ * Replaces sonicmoe::_down_projection_forward (sonicmoe/functional/forward.py:132-175). */
+int smoe_down_projection_forward(const void* y1, const void* w2, void* y2, const int* expert_offset, int H, int I,
+                                 int E, int TK, int* status, void* stream);
+
+/* Fused down projection + router-weighted scatter-reduce: o_acc[x_gather_idx[r], :] += score(r) * (y1[r] @ W2[e]^T)
+ * with fp32 atomics; o_acc (T,H) fp32 must be zero on entry.  score(r) = scores[s_scatter_idx[r]].
+ * Replaces _down_projection_forward followed by _router_forward (sonicmoe/functional/forward.py:132-202). */
+int smoe_down_projection_forward_scatter(const void* y1, const void* w2, float* o_acc, const void* scores,
+                                         int scores_are_bf16, const int* expert_offset, const int* x_gather_idx,
+                                         const int* s_scatter_idx, int T, int H, int I, int E, int TK, int* status,
+                                         void* stream);
+
+/* dy1 = dout[x_gather_idx[r]] @ W2[e]; y1 recomputed from z; dz = dswiglu(z) * dy1 * s, y1s = y1 * s,
+ * ds_partial[c, r] = sum over the c-th 256-column block of dy1 * y1.  ds_partial has
+ * smoe_ds_partial_columns(I) * TK floats.  Replaces the dz kernel of sonicmoe::_down_projection_backward
+ * (sonicmoe/functional/backward.py:286-389). */
+int smoe_down_projection_backward_act(const void* dout, const void* w2, const void* z, const void* scores,
+                                      int scores_are_bf16, void* dz, void* y1s, float* ds_partial,
+                                      const int* expert_offset, const int* x_gather_idx, const int* s_scatter_idx,
+                                      int T, int H, int I, int E, int TK, int* status, void* stream);
+int smoe_ds_partial_columns(int I);
+
+/* dx_expanded[r, :] = dz[r, :] @ W1[e].  dx_expanded (TK,H).
+ * Replaces the dx kernel of sonicmoe::_up_projection_backward (sonicmoe/functional/backward.py:259-280). */
+int smoe_up_projection_backward_dx(const void* dz, const void* w1, void* dx_expanded, const int* expert_offset, int H,
+                                   int I, int E, int TK, int* status, void* stream);
+
+/* dW2[e] (H,I) = sum over rows r of expert e of dout[x_gather_idx[r], :]^T y1s[r, :]; zeros for an empty expert.
+ * Replaces the dw2 kernel of sonicmoe::_down_projection_backward (sonicmoe/functional/backward.py:438-458). */
+int smoe_down_projection_weight_grad(const void* dout, const void* y1s, void* dw2, const int* expert_offset,
+                                     const int* x_gather_idx, int T, int H, int I, int E, int TK, int* status,
+                                     void* stream);
+
+/* dW1[e] (2I,H) = sum over rows r of expert e of dz[r, :]^T x[x_gather_idx[r], :].
+ * Replaces the dw1 kernel of sonicmoe::_up_projection_backward (sonicmoe/functional/backward.py:237-257). */
+int smoe_up_projection_weight_grad(const void* x, const void* dz, void* dw1, const int* expert_offset,
+                                   const int* x_gather_idx, int T, int H, int I, int E, int TK, int* status,
+                                   void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SONICMOE_B200_H_ */

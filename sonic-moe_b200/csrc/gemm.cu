@@ -1,0 +1,212 @@
+// Host side of the grouped GEMMs: tensor-map construction and the C-ABI launchers.
+#include "gemm.cuh"
+
+#include <mutex>
+
+#include "../../include/sonicmoe_b200.h"
+
+namespace smoe {
+
+// cuTensorMapEncodeTiled is fetched through the runtime so that the library links against cudart
+// only and still loads on a machine without a driver.
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+  });
+  return fn;
+}
+
+// bf16 row-major 2D tensor (rows, cols) with a row pitch in elements; box = (box_rows, box_cols),
+// 128-byte swizzle, out-of-bounds elements read as zero.
+static int encode_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t pitch_elems,
+                     uint32_t box_rows, uint32_t box_cols) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) return SMOE_ERR_DRIVER;
+  if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0 || (pitch_elems * 2) % 16 != 0) return SMOE_ERR_ALIGNMENT;
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {pitch_elems * 2};
+  const cuuint32_t box[2] = {box_cols, box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? SMOE_OK : SMOE_ERR_TENSORMAP;
+}
+
+static int num_sms() {
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) sms = 0;
+  }
+  return sms;
+}
+
+template <bool RAGGED_K, bool A_GATHER, bool A_MN, bool B_GATHER, bool B_MN, int EPI>
+static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, cudaStream_t stream) {
+  auto kernel = grouped_gemm_kernel<RAGGED_K, A_GATHER, A_MN, B_GATHER, B_MN, EPI>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_BYTES) != cudaSuccess)
+      return SMOE_ERR_LAUNCH;
+    configured = true;
+  }
+  const int sms = num_sms();
+  if (sms <= 0) return SMOE_ERR_DRIVER;
+  kernel<<<sms, GEMM_THREADS, GEMM_SMEM_BYTES, stream>>>(tmA, tmB, p);
+  return cudaGetLastError() == cudaSuccess ? SMOE_OK : SMOE_ERR_LAUNCH;
+}
+
+static bool bad_shape(int H, int I, int E) {
+  return H <= 0 || I <= 0 || E <= 0 || E > MAX_EXPERTS || (H % 64) != 0 || (I % 64) != 0;
+}
+
+}  // namespace smoe
+
+using namespace smoe;
+
+#define SMOE_TRY(expr)              \
+  do {                              \
+    const int _rc = (expr);         \
+    if (_rc != SMOE_OK) return _rc; \
+  } while (0)
+
+extern "C" {
+
+int smoe_up_projection_forward(const void* x, const void* w1, void* z, void* y1, const int* expert_offset,
+                               const int* x_gather_idx, int T, int H, int I, int E, int TK, int* status,
+                               void* stream) {
+  if (bad_shape(H, I, E) || T <= 0 || TK < 0) return SMOE_ERR_SHAPE;
+  if (TK == 0) return SMOE_OK;
+  CUtensorMap tmA, tmB;
+  SMOE_TRY(encode_2d(&tmA, x, T, H, H, 1, BK));                        // gather4 rows of x
+  SMOE_TRY(encode_2d(&tmB, w1, (uint64_t)E * 2 * I, H, H, BN, BK));    // W1[e] rows = output features, K-major
+  GemmParams p = {};
+  p.E = E; p.N = 2 * I; p.K = H; p.total_rows = TK; p.gather_rows = T; p.b_rows_per_expert = 2 * I;
+  p.off = expert_offset; p.gather = x_gather_idx;
+  p.out0 = static_cast<__nv_bfloat16*>(z); p.ld0 = 2 * I;
+  p.out1 = static_cast<__nv_bfloat16*>(y1); p.ld1 = I;
+  p.status = status;
+  return launch<false, true, false, false, false, EPI_SWIGLU>(tmA, tmB, p, static_cast<cudaStream_t>(stream));
+}
+
+int smoe_down_projection_forward(const void* y1, const void* w2, void* y2, const int* expert_offset, int H, int I,
+                                 int E, int TK, int* status, void* stream) {
+  if (bad_shape(H, I, E) || TK < 0) return SMOE_ERR_SHAPE;
+  if (TK == 0) return SMOE_OK;
+  CUtensorMap tmA, tmB;
+  SMOE_TRY(encode_2d(&tmA, y1, TK, I, I, BM, BK));
+  SMOE_TRY(encode_2d(&tmB, w2, (uint64_t)E * H, I, I, BN, BK));        // W2[e] is (H, I): K-major
+  GemmParams p = {};
+  p.E = E; p.N = H; p.K = I; p.total_rows = TK; p.b_rows_per_expert = H;
+  p.off = expert_offset;
+  p.out0 = static_cast<__nv_bfloat16*>(y2); p.ld0 = H;
+  p.status = status;
+  return launch<false, false, false, false, false, EPI_STORE>(tmA, tmB, p, static_cast<cudaStream_t>(stream));
+}
+
+int smoe_down_projection_forward_scatter(const void* y1, const void* w2, float* o_acc, const void* scores,
+                                         int scores_are_bf16, const int* expert_offset, const int* x_gather_idx,
+                                         const int* s_scatter_idx, int T, int H, int I, int E, int TK, int* status,
+                                         void* stream) {
+  if (bad_shape(H, I, E) || TK < 0 || T <= 0) return SMOE_ERR_SHAPE;
+  if (TK == 0) return SMOE_OK;
+  CUtensorMap tmA, tmB;
+  SMOE_TRY(encode_2d(&tmA, y1, TK, I, I, BM, BK));
+  SMOE_TRY(encode_2d(&tmB, w2, (uint64_t)E * H, I, I, BN, BK));
+  GemmParams p = {};
+  p.E = E; p.N = H; p.K = I; p.total_rows = TK; p.gather_rows = T; p.b_rows_per_expert = H;
+  p.off = expert_offset; p.gather = x_gather_idx; p.s_scatter = s_scatter_idx;
+  p.scores = scores; p.scores_are_bf16 = scores_are_bf16; p.acc_out = o_acc;
+  p.status = status;
+  return launch<false, false, false, false, false, EPI_SCATTER>(tmA, tmB, p, static_cast<cudaStream_t>(stream));
+}
+
+int smoe_down_projection_backward_act(const void* dout, const void* w2, const void* z, const void* scores,
+                                      int scores_are_bf16, void* dz, void* y1s, float* ds_partial,
+                                      const int* expert_offset, const int* x_gather_idx, const int* s_scatter_idx,
+                                      int T, int H, int I, int E, int TK, int* status, void* stream) {
+  if (bad_shape(H, I, E) || TK < 0 || T <= 0) return SMOE_ERR_SHAPE;
+  if (TK == 0) return SMOE_OK;
+  CUtensorMap tmA, tmB;
+  SMOE_TRY(encode_2d(&tmA, dout, T, H, H, 1, BK));                     // gather4 rows of dout
+  SMOE_TRY(encode_2d(&tmB, w2, (uint64_t)E * H, I, I, BK, 64));        // W2[e] (H, I): rows are k, MN-major
+  GemmParams p = {};
+  p.E = E; p.N = I; p.K = H; p.total_rows = TK; p.gather_rows = T; p.b_rows_per_expert = H;
+  p.off = expert_offset; p.gather = x_gather_idx; p.s_scatter = s_scatter_idx;
+  p.out0 = static_cast<__nv_bfloat16*>(dz); p.ld0 = 2 * I;
+  p.out1 = static_cast<__nv_bfloat16*>(y1s); p.ld1 = I;
+  p.z = static_cast<const __nv_bfloat16*>(z);
+  p.scores = scores; p.scores_are_bf16 = scores_are_bf16; p.ds_partial = ds_partial;
+  p.status = status;
+  return launch<false, true, false, false, true, EPI_DSWIGLU>(tmA, tmB, p, static_cast<cudaStream_t>(stream));
+}
+
+int smoe_ds_partial_columns(int I) { return (I + BN - 1) / BN; }
+
+int smoe_up_projection_backward_dx(const void* dz, const void* w1, void* dx_expanded, const int* expert_offset, int H,
+                                   int I, int E, int TK, int* status, void* stream) {
+  if (bad_shape(H, I, E) || TK < 0) return SMOE_ERR_SHAPE;
+  if (TK == 0) return SMOE_OK;
+  CUtensorMap tmA, tmB;
+  SMOE_TRY(encode_2d(&tmA, dz, TK, 2 * I, 2 * I, BM, BK));
+  SMOE_TRY(encode_2d(&tmB, w1, (uint64_t)E * 2 * I, H, H, BK, 64));    // W1[e] (2I, H): rows are k, MN-major
+  GemmParams p = {};
+  p.E = E; p.N = H; p.K = 2 * I; p.total_rows = TK; p.b_rows_per_expert = 2 * I;
+  p.off = expert_offset;
+  p.out0 = static_cast<__nv_bfloat16*>(dx_expanded); p.ld0 = H;
+  p.status = status;
+  return launch<false, false, false, false, true, EPI_STORE>(tmA, tmB, p, static_cast<cudaStream_t>(stream));
+}
+
+int smoe_down_projection_weight_grad(const void* dout, const void* y1s, void* dw2, const int* expert_offset,
+                                     const int* x_gather_idx, int T, int H, int I, int E, int TK, int* status,
+                                     void* stream) {
+  if (bad_shape(H, I, E) || TK < 0 || T <= 0) return SMOE_ERR_SHAPE;
+  if (TK == 0) {
+    return cudaMemsetAsync(dw2, 0, (size_t)E * H * I * 2, static_cast<cudaStream_t>(stream)) == cudaSuccess
+               ? SMOE_OK : SMOE_ERR_LAUNCH;
+  }
+  CUtensorMap tmA, tmB;
+  SMOE_TRY(encode_2d(&tmA, dout, T, H, H, 1, 64));                     // A[h, t] = dout[gather[t], h]
+  SMOE_TRY(encode_2d(&tmB, y1s, TK, I, I, BK, 64));                    // B[i, t] = y1s[t, i]
+  GemmParams p = {};
+  p.E = E; p.M = H; p.N = I; p.total_rows = TK; p.gather_rows = T;
+  p.off = expert_offset; p.gather = x_gather_idx;
+  p.out0 = static_cast<__nv_bfloat16*>(dw2); p.ld0 = I; p.out0_expert_stride = (long long)H * I;
+  p.status = status;
+  return launch<true, true, true, false, true, EPI_STORE>(tmA, tmB, p, static_cast<cudaStream_t>(stream));
+}
+
+int smoe_up_projection_weight_grad(const void* x, const void* dz, void* dw1, const int* expert_offset,
+                                   const int* x_gather_idx, int T, int H, int I, int E, int TK, int* status,
+                                   void* stream) {
+  if (bad_shape(H, I, E) || TK < 0 || T <= 0) return SMOE_ERR_SHAPE;
+  if (TK == 0) {
+    return cudaMemsetAsync(dw1, 0, (size_t)E * 2 * I * H * 2, static_cast<cudaStream_t>(stream)) == cudaSuccess
+               ? SMOE_OK : SMOE_ERR_LAUNCH;
+  }
+  CUtensorMap tmA, tmB;
+  SMOE_TRY(encode_2d(&tmA, dz, TK, 2 * I, 2 * I, BK, 64));             // A[j, t] = dz[t, j]
+  SMOE_TRY(encode_2d(&tmB, x, T, H, H, 1, 64));                        // B[h, t] = x[gather[t], h]
+  GemmParams p = {};
+  p.E = E; p.M = 2 * I; p.N = H; p.total_rows = TK; p.gather_rows = T;
+  p.off = expert_offset; p.gather = x_gather_idx;
+  p.out0 = static_cast<__nv_bfloat16*>(dw1); p.ld0 = H; p.out0_expert_stride = (long long)2 * I * H;
+  p.status = status;
+  return launch<true, false, true, true, true, EPI_STORE>(tmA, tmB, p, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"
