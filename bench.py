@@ -1,0 +1,419 @@
+"""Benchmark of the MoE-layer hot path (forward + backward) on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+Workload: BASELINE configs[1] — T=32768 tokens, H=4096, I=1024, E=128 experts, top-K=8, SwiGLU, bf16,
+token-choice softmax top-k routing; weights iid N(0, 0.02), x and upstream gradient iid N(0, 1), seeded,
+synthetic.  One step = one forward + backward of the layer through `sonicmoe.MoE` (all gradients: x,
+router, up and down projections).  FLOP model of the reference benchmark: 18 * T*K * I * H per step
+(benchmarks/moe-cute.py:231-234, 297-300); router GEMM, softmax and combine are timed but not counted.
+
+With N > 1 every rank runs the whole layer on its own T tokens (replicas, weak scaling, no data-path
+collective); `value` is the sum over ranks.
+
+Prints ONE JSON line (rank 0).  `--impl reference` times the CPU oracle (a port of the reference's
+torch-eager layer) on the host cores on a bounded sample of the same workload.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for _p in (ROOT, os.path.join(ROOT, "sonic-moe_b200")):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+import torch  # noqa: E402
+
+CFG = dict(T=32768, H=4096, I=1024, E=128, K=8)
+CPU_SAMPLE_TOKENS = 512  # tokens of the same layer shape the CPU baseline processes per step
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def flops_per_step(T, H, I, K):
+    return 18.0 * T * K * I * H
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {k: float(p[k]) for k in FALLBACK_PEAKS if k in p} | {"source": "measured"}
+    return dict(FALLBACK_PEAKS, source="fallback")
+
+
+# --------------------------------------------------------------------------------------------------
+# clocks
+# --------------------------------------------------------------------------------------------------
+class ClockSampler:
+    """Samples nvidia-smi while the timed region runs (read-only queries)."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.rows: list[list[str]] = []
+        self.proc = None
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.gpu_index), f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._pump, daemon=True)
+        self.thread.start()
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) >= 7:
+                self.rows.append(parts)
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()  # the exact process started above
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[0]))
+                mx.append(float(r[1]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# --------------------------------------------------------------------------------------------------
+# the CPU arm (oracle port of the reference's torch-eager layer)
+# --------------------------------------------------------------------------------------------------
+def cpu_sample_inputs(cfg, tokens, device_for_rng):
+    """fp32 weights of the full layer and `tokens` tokens, values as in the GPU arm (N(0,.02) / N(0,1))."""
+    H, I, E = cfg["H"], cfg["I"], cfg["E"]
+    g = torch.Generator(device=device_for_rng).manual_seed(0)
+
+    def rn(*shape, std):
+        t = torch.randn(*shape, generator=g, device=device_for_rng, dtype=torch.float32) * std
+        return t.bfloat16().float().cpu()
+
+    return dict(router_w=rn(E, H, std=0.02), w1=rn(E, 2 * I, H, std=0.02), w2=rn(E, H, I, std=0.02),
+                x=rn(tokens, H, std=1.0), dout=rn(tokens, H, std=1.0))
+
+
+def cpu_step(inp, K):
+    from oracle import moe_oracle as orc
+
+    t0 = time.perf_counter()
+    orc.moe_layer(inp["x"], inp["router_w"], inp["w1"], inp["w2"], K, dout=inp["dout"])
+    return time.perf_counter() - t0
+
+
+def run_reference_arm(args, rank, world):
+    if rank != 0:
+        return
+    cfg = CFG
+    torch.set_num_threads(os.cpu_count() or 1)
+    rng_dev = "cuda" if torch.cuda.is_available() else "cpu"
+    inp = cpu_sample_inputs(cfg, CPU_SAMPLE_TOKENS, rng_dev)
+    for _ in range(args.warmup):
+        cpu_step(inp, cfg["K"])
+    times = [cpu_step(inp, cfg["K"]) for _ in range(args.steps)]
+    dt = sum(times) / len(times)
+    fl = flops_per_step(CPU_SAMPLE_TOKENS, cfg["H"], cfg["I"], cfg["K"])
+    value = fl / dt / 1e12
+    sample = (f"{CPU_SAMPLE_TOKENS} tokens per step of the same layer (H{cfg['H']} I{cfg['I']} E{cfg['E']} "
+              f"K{cfg['K']}), fp32, forward+backward with all gradients")
+    line = {
+        "impl": "reference", "metric": "moe_fwd_bwd_tflops", "value": value, "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "tokens_per_s": CPU_SAMPLE_TOKENS / dt,
+        "config": workload_config(args.gpus),
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(n_gpus):
+    return {"workload": "moe_layer_fwd_bwd_top8_of_128_T32768_H4096_I1024_swiglu_bf16", **CFG,
+            "routing": "softmax_topk", "parallelism": f"replicas{n_gpus}",
+            "l2_policy": "inputs larger than L2 (weights 3 GiB, activations > 1 GiB per step)"}
+
+
+# --------------------------------------------------------------------------------------------------
+# the GPU arm
+# --------------------------------------------------------------------------------------------------
+def build_layer(cfg, dev):
+    import sonicmoe
+    from sonicmoe.enums import ActivationType
+
+    torch.manual_seed(0)
+    torch.cuda.manual_seed(0)
+    with torch.device(dev):
+        moe = sonicmoe.MoE(cfg["E"], cfg["K"], cfg["H"], cfg["I"], ActivationType.SWIGLU, False, 0.02)
+        torch.nn.init.normal_(moe.router.weight, 0.0, 0.02)
+    return moe.to(torch.bfloat16)
+
+
+def zero_grads(moe, x):
+    x.grad = None
+    for p in moe.parameters():
+        p.grad = None
+
+
+def time_kernels(moe, x, dout, cfg, peaks):
+    """CUDA-event time of each grouped GEMM launched alone on the benchmark's tensors (inputs far larger than
+    L2), and of the two gather-sum reductions; returns per-kernel figures and the dominant GEMM."""
+    from sonicmoe import _lib, functional as fn
+
+    lib = _lib.lib
+    dev = x.device
+    T, H, I, E, K = (cfg[k] for k in "THIEK")
+    TK = T * K
+    st = _lib.device_state(dev).status.data_ptr()
+    stream = torch.cuda.current_stream().cuda_stream
+    with torch.no_grad():
+        logits = torch.nn.functional.linear(x, moe.router.weight)
+        scores, idx = fn.topk_softmax(logits, K)
+        route = fn._route_metadata(idx.reshape(-1), None, E, K)
+    off, gat, sct, rev = (route.expert_frequency_offset.data_ptr(), route.x_gather_idx.data_ptr(),
+                          route.s_scatter_idx.data_ptr(), route.s_reverse_scatter_idx.data_ptr())
+    bf = dict(dtype=torch.bfloat16, device=dev)
+    w1, w2 = moe.c_fc.weight.detach(), moe.c_proj.weight.detach()
+    z = torch.empty(TK, 2 * I, **bf); y1 = torch.empty(TK, I, **bf); y2 = torch.empty(TK, H, **bf)
+    dz = torch.empty(TK, 2 * I, **bf); y1s = torch.empty(TK, I, **bf); o = torch.empty(T, H, **bf)
+    dw1 = torch.empty_like(w1); dw2 = torch.empty_like(w2)
+    ncols = lib.smoe_ds_partial_columns(I)
+    dsp = torch.empty(ncols, TK, dtype=torch.float32, device=dev)
+    sc = scores.reshape(-1)
+    unit = 2.0 * TK * I * H  # flops of one TK x I x H contraction
+    ops = {
+        "up_projection_forward": (2 * unit, lambda: lib.smoe_up_projection_forward(
+            x.data_ptr(), w1.data_ptr(), z.data_ptr(), y1.data_ptr(), off, gat, T, H, I, E, TK, st, stream)),
+        "down_projection_forward": (unit, lambda: lib.smoe_down_projection_forward(
+            y1.data_ptr(), w2.data_ptr(), y2.data_ptr(), off, H, I, E, TK, st, stream)),
+        "down_projection_backward_act": (unit, lambda: lib.smoe_down_projection_backward_act(
+            dout.data_ptr(), w2.data_ptr(), z.data_ptr(), sc.data_ptr(), 0, dz.data_ptr(), y1s.data_ptr(),
+            dsp.data_ptr(), off, gat, sct, T, H, I, E, TK, st, stream)),
+        "down_projection_weight_grad": (unit, lambda: lib.smoe_down_projection_weight_grad(
+            dout.data_ptr(), y1s.data_ptr(), dw2.data_ptr(), off, gat, T, H, I, E, TK, st, stream)),
+        "up_projection_weight_grad": (2 * unit, lambda: lib.smoe_up_projection_weight_grad(
+            x.data_ptr(), dz.data_ptr(), dw1.data_ptr(), off, gat, T, H, I, E, TK, st, stream)),
+        "up_projection_backward_dx": (2 * unit, lambda: lib.smoe_up_projection_backward_dx(
+            dz.data_ptr(), w1.data_ptr(), y2.data_ptr(), off, H, I, E, TK, st, stream)),
+    }
+    gather_bytes = TK * H * 2 + T * H * 2 + TK * 8
+    hbm_ops = {
+        "gather_sum_weighted": (gather_bytes, lambda: lib.smoe_gather_sum(
+            y2.data_ptr(), o.data_ptr(), sc.data_ptr(), _lib.SMOE_F32, rev, None, T, H, K, stream)),
+        "gather_sum_plain": (gather_bytes, lambda: lib.smoe_gather_sum(
+            y2.data_ptr(), o.data_ptr(), None, 0, rev, None, T, H, K, stream)),
+    }
+    out = {}
+    reps = 5
+
+    def timed(fn_):
+        fn_()  # warm
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            rc = fn_()
+            assert rc == 0, rc
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps
+
+    for name, (fl, f) in ops.items():
+        ms = timed(f)
+        tf = fl / (ms * 1e-3) / 1e12
+        out[name] = {"ms": round(ms, 4), "tflops": round(tf, 1), "frac_of_bf16_peak": round(tf / peaks["bf16_tflops"], 3)}
+    for name, (by, f) in hbm_ops.items():
+        ms = timed(f)
+        gbs = by / (ms * 1e-3) / 1e9
+        out[name] = {"ms": round(ms, 4), "gbs": round(gbs, 1), "frac_of_hbm_peak": round(gbs / peaks["hbm_gbs"], 3)}
+    _lib.check_status(dev)
+    dominant = max(ops, key=lambda n: out[n]["ms"])
+    return out, dominant, ops[dominant][0]
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu capture summarised under profiles/
+# (None until a capture exists for the kernel).
+NCU_TRAFFIC_BYTES = {}
+
+
+def run_gpu_arm(args, rank, world, local_rank):
+    from sonicmoe import _lib
+
+    cfg = CFG
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    distributed = world > 1
+    if distributed:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=dev)
+    peaks = load_peaks()
+    T, H, I, E, K = (cfg[k] for k in "THIEK")
+
+    moe = build_layer(cfg, dev)
+    g = torch.Generator(device=dev).manual_seed(1234 + rank)
+    x_host = torch.randn(T, H, generator=g, device=dev).bfloat16().cpu().pin_memory()
+    dout_host = torch.randn(T, H, generator=g, device=dev).bfloat16().cpu().pin_memory()
+    x = x_host.to(dev, non_blocking=True).requires_grad_(True)
+    dout = dout_host.to(dev, non_blocking=True)
+    o_host = torch.empty(T, H, dtype=torch.bfloat16).pin_memory()
+    dx_host = torch.empty(T, H, dtype=torch.bfloat16).pin_memory()
+
+    def step_resident():
+        zero_grads(moe, x)
+        o, _aux = moe(x)
+        o.backward(dout)
+
+    def step_e2e():
+        xs = x_host.to(dev, non_blocking=True).requires_grad_(True)
+        ds = dout_host.to(dev, non_blocking=True)
+        for p in moe.parameters():
+            p.grad = None
+        o, _aux = moe(xs)
+        o.backward(ds)
+        o_host.copy_(o.detach(), non_blocking=True)
+        dx_host.copy_(xs.grad, non_blocking=True)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if distributed:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed_region(fn, steps):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        barrier()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if distributed:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return ms.item()
+
+    for _ in range(max(args.warmup, 3)):
+        step_resident()
+    _lib.check_status(dev)
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    launches_before = _lib.launch_count()
+    total_ms = timed_region(step_resident, args.steps)
+    launches = _lib.launch_count() - launches_before
+    clocks = sampler.stop() if rank == 0 else None
+    _lib.check_status(dev)
+
+    for _ in range(2):
+        step_e2e()
+    e2e_ms = timed_region(step_e2e, args.steps)
+    _lib.check_status(dev)
+
+    ms_per_step = total_ms / args.steps
+    fl = flops_per_step(T, H, I, K)
+    value = world * fl / (ms_per_step * 1e-3) / 1e12
+    e2e_value = world * fl / (e2e_ms / args.steps * 1e-3) / 1e12
+
+    if rank != 0:
+        if distributed:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
+
+    kernels, dominant, dom_flops = time_kernels(moe, x.detach(), dout, cfg, peaks)
+    achieved = kernels[dominant]["tflops"]
+    roofline = {"bound": "tensor", "kernel": dominant, "achieved": achieved, "peak": peaks["bf16_tflops"],
+                "unit": "TFLOP/s", "frac": round(achieved / peaks["bf16_tflops"], 3),
+                "peak_source": f"{peaks['source']} cuBLAS bf16 burst", "flops_per_launch": dom_flops,
+                "traffic": NCU_TRAFFIC_BYTES.get(dominant),
+                "layer_frac_of_sustained_peak": round(value / world / peaks["bf16_tflops_sustained"], 3)}
+
+    cpu_baseline = None
+    if world == 1:
+        torch.set_num_threads(os.cpu_count() or 1)
+        inp = cpu_sample_inputs(cfg, CPU_SAMPLE_TOKENS, dev)
+        cpu_step(inp, K)  # warm
+        dt = min(cpu_step(inp, K) for _ in range(2))
+        cpu_baseline = {
+            "value": flops_per_step(CPU_SAMPLE_TOKENS, H, I, K) / dt / 1e12, "unit": "TFLOP/s",
+            "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"{CPU_SAMPLE_TOKENS} tokens of the same layer shape, fp32 oracle forward+backward, "
+                      f"{dt * 1e3:.0f} ms"}
+
+    line = {
+        "metric": "moe_fwd_bwd_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "tokens_per_s": world * T / (ms_per_step * 1e-3),
+        "tflops_per_gpu": value / world,
+        "config": workload_config(world),
+        "clocks": clocks,
+        "e2e": {"value": e2e_value, "unit": "TFLOP/s", "ms_per_step": e2e_ms / args.steps,
+                "h2d_bytes_per_step": 2 * T * H * 2, "d2h_bytes_per_step": 2 * T * H * 2,
+                "api": "sonicmoe.MoE.forward + backward; x and dout from pinned host memory, o and dx read back"},
+        "gpu_launches": launches,
+        "roofline": roofline,
+        "kernels": kernels,
+        "cpu_baseline": cpu_baseline,
+    }
+    print(json.dumps(line), flush=True)
+    if distributed:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference_arm(args, rank, world)
+        return
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the layer has no CPU path (use --impl reference for the CPU arm)")
+    run_gpu_arm(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

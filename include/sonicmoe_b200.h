@@ -46,6 +46,64 @@ enum { SMOE_F32 = 0, SMOE_BF16 = 1, SMOE_I32 = 2, SMOE_I64 = 3 };
 int smoe_abi_version(void);
 
 /* ---------------------------------------------------------------------------------------------
+ * Router: top-k, softmax over the winners, histogram / prefix sum, grouped-row index vectors
+ * ------------------------------------------------------------------------------------------- */
+
+/* Per row of logits (T,E) [SMOE_F32 or SMOE_BF16]: the K largest values, largest first, equal values
+ * ordered by lower column; scores (T,K) fp32 = softmax over those K values; indices (T,K) int32.
+ * Replaces sonicmoe::_softmax_topk_fwd / _topk_fwd (sonicmoe/functional/forward.py:20-50, 224-237;
+ * kernel sonicmoe/functional/topk_softmax.py:86-193). */
+int smoe_topk_softmax(const void* logits, int logits_dtype, float* scores, int* indices, int T, int E, int K,
+                      void* stream);
+
+/* dlogits (T,E) [SMOE_F32 or SMOE_BF16], every element written: dlogits[t, indices[t,k]] =
+ * score[t,k] * (dscore[t,k] - sum_j dscore[t,j] score[t,j]), zero elsewhere.
+ * Replaces sonicmoe::_softmax_topk_bwd (sonicmoe/functional/backward.py:488-556) and the zero fill
+ * before it (sonicmoe/functional/__init__.py:107). */
+int smoe_softmax_topk_backward(void* dlogits, int dlogits_dtype, const float* dscore, const float* score,
+                               const int* indices, int T, int E, int K, void* stream);
+
+/* count[e] = #{i : x[i] == e}, cumsum[e] = count[0] + ... + count[e] (cumsum may be NULL); x is
+ * SMOE_I32 or SMOE_I64 of length n; ids outside [0,E) are ignored.  workspace: device scratch of
+ * smoe_count_cumsum_workspace_bytes(E) bytes (needed for E <= 4096).
+ * Replaces sonicmoe::count_cumsum_cuda (sonicmoe/count_cumsum/__init__.py:11-29, kernel.cu:93-203). */
+size_t smoe_count_cumsum_workspace_bytes(int E);
+int smoe_count_cumsum(const void* x, int x_dtype, long long n, int E, int* count, int* cumsum, void* workspace,
+                      void* stream);
+
+/* From the flat expert id of each of n routed pairs: expert_count (E), expert_offset (E+1, leading 0),
+ * and a stable counting sort by expert: s_scatter_idx[r] = flat slot of grouped row r,
+ * s_reverse_scatter_idx[slot] = r, x_gather_idx[r] = token of row r (slot / K, or token_idx[slot] when
+ * token_idx != NULL).  E <= 4096.  workspace: smoe_route_metadata_workspace_bytes(E) bytes.
+ * Replaces count_cumsum + TC_topk_router_metadata / general_routing_router_metadata
+ * (sonicmoe/functional/__init__.py:19-82). */
+size_t smoe_route_metadata_workspace_bytes(int E);
+int smoe_route_metadata(const int* expert_idx, const int* token_idx, long long n, int E, int K, int* expert_count,
+                        int* expert_offset, int* s_scatter_idx, int* s_reverse_scatter_idx, int* x_gather_idx,
+                        void* workspace, void* stream);
+
+/* offsets[t] = number of entries of the ascending vector sorted_idx (length n) that are < t, t = 0..T.
+ * Replaces the per-token count_cumsum / bincount of general_routing_router_metadata
+ * (sonicmoe/functional/__init__.py:66-73). */
+int smoe_sorted_offsets(const int* sorted_idx, long long n, int T, int* offsets, void* stream);
+
+/* out[t,:] = sum over p in [token_offset[t], token_offset[t+1]) (or [t*K, (t+1)*K) when token_offset is
+ * NULL) of weights[p] * src[reverse_idx[p], :]; weights NULL = 1, else SMOE_F32 / SMOE_BF16; src, out
+ * bf16 with H columns; fp32 accumulation.  Replaces sonicmoe::_router_forward and
+ * sonicmoe::_token_broadcast_backward (sonicmoe/functional/forward.py:181-202, backward.py:464-484;
+ * kernel sonicmoe/functional/reduction_over_k_gather.py:447-556). */
+int smoe_gather_sum(const void* src, void* out, const void* weights, int weights_dtype, const int* reverse_idx,
+                    const int* token_offset, int T, int H, int K, void* stream);
+
+/* dst (bf16) = src (fp32), n elements, n % 8 == 0: finishes the fused scatter-reduce output. */
+int smoe_cast_f32_to_bf16(const float* src, void* dst, long long n, void* stream);
+
+/* ds[s_scatter_idx[r]] = sum_c ds_partial[c, r]; ds is SMOE_F32 or SMOE_BF16.
+ * Replaces the ds_partial reduction of _down_projection_backward (sonicmoe/functional/backward.py:391-408). */
+int smoe_ds_reduce(const float* ds_partial, const int* s_scatter_idx, void* ds, int ds_dtype, int TK, int ncols,
+                   void* stream);
+
+/* ---------------------------------------------------------------------------------------------
  * Grouped GEMMs (tcgen05 / TMEM / TMA)
  * ------------------------------------------------------------------------------------------- */
 

@@ -1,6 +1,8 @@
 // Host side of the grouped GEMMs: tensor-map construction and the C-ABI launchers.
 #include "gemm.cuh"
 
+#include <cstdio>
+#include <cstdlib>
 #include <mutex>
 
 #include "../../include/sonicmoe_b200.h"
@@ -33,6 +35,14 @@ static int encode_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t
                      uint32_t box_rows, uint32_t box_cols) {
   EncodeTiledFn fn = get_encode_fn();
   if (fn == nullptr) return SMOE_ERR_DRIVER;
+  // The encoder is a driver-API call and needs the device's primary context current on the calling
+  // thread; a thread that has made no runtime call yet (an autograd worker) has none.  A no-op runtime
+  // call binds it.
+  static thread_local bool context_bound = false;
+  if (!context_bound) {
+    if (cudaFree(nullptr) != cudaSuccess) return SMOE_ERR_DRIVER;
+    context_bound = true;
+  }
   if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0 || (pitch_elems * 2) % 16 != 0) return SMOE_ERR_ALIGNMENT;
   const cuuint64_t dims[2] = {cols, rows};
   const cuuint64_t strides[1] = {pitch_elems * 2};
@@ -41,6 +51,11 @@ static int encode_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t
   const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS && getenv("SMOE_DEBUG") != nullptr) {
+    fprintf(stderr, "smoe: cuTensorMapEncodeTiled failed (CUresult %d): base=%p rows=%llu cols=%llu pitch=%llu box=(%u,%u)\n",
+            static_cast<int>(r), base, (unsigned long long)rows, (unsigned long long)cols,
+            (unsigned long long)pitch_elems, box_rows, box_cols);
+  }
   return r == CUDA_SUCCESS ? SMOE_OK : SMOE_ERR_TENSORMAP;
 }
 
@@ -54,9 +69,19 @@ static int num_sms() {
   return sms;
 }
 
-template <bool RAGGED_K, bool A_GATHER, bool A_MN, bool B_GATHER, bool B_MN, int EPI>
-static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, cudaStream_t stream) {
-  auto kernel = grouped_gemm_kernel<RAGGED_K, A_GATHER, A_MN, B_GATHER, B_MN, EPI>;
+// Gathered operands are fetched by cp.async warps (default) or, with SMOE_TMA_GATHER=1 in the
+// environment, by TMA tile::gather4 from the producer warp.
+static bool use_tma_gather() {
+  static const bool v = [] {
+    const char* e = getenv("SMOE_TMA_GATHER");
+    return e != nullptr && e[0] == '1';
+  }();
+  return v;
+}
+
+template <bool RAGGED_K, bool A_GATHER, bool A_MN, bool B_GATHER, bool B_MN, int EPI, bool LSU_GATHER>
+static int launch_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, cudaStream_t stream) {
+  auto kernel = grouped_gemm_kernel<RAGGED_K, A_GATHER, A_MN, B_GATHER, B_MN, EPI, LSU_GATHER>;
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_BYTES) != cudaSuccess)
@@ -65,8 +90,19 @@ static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmPara
   }
   const int sms = num_sms();
   if (sms <= 0) return SMOE_ERR_DRIVER;
-  kernel<<<sms, GEMM_THREADS, GEMM_SMEM_BYTES, stream>>>(tmA, tmB, p);
+  constexpr int threads = (LSU_GATHER && (A_GATHER || B_GATHER)) ? GEMM_THREADS + GATHER_THREADS : GEMM_THREADS;
+  kernel<<<sms, threads, GEMM_SMEM_BYTES, stream>>>(tmA, tmB, p);
   return cudaGetLastError() == cudaSuccess ? SMOE_OK : SMOE_ERR_LAUNCH;
+}
+
+template <bool RAGGED_K, bool A_GATHER, bool A_MN, bool B_GATHER, bool B_MN, int EPI>
+static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, cudaStream_t stream) {
+  if constexpr (A_GATHER || B_GATHER) {
+    if (use_tma_gather()) return launch_variant<RAGGED_K, A_GATHER, A_MN, B_GATHER, B_MN, EPI, false>(tmA, tmB, p, stream);
+    return launch_variant<RAGGED_K, A_GATHER, A_MN, B_GATHER, B_MN, EPI, true>(tmA, tmB, p, stream);
+  } else {
+    return launch_variant<RAGGED_K, A_GATHER, A_MN, B_GATHER, B_MN, EPI, false>(tmA, tmB, p, stream);
+  }
 }
 
 static bool bad_shape(int H, int I, int E) {
@@ -96,6 +132,7 @@ int smoe_up_projection_forward(const void* x, const void* w1, void* z, void* y1,
   GemmParams p = {};
   p.E = E; p.N = 2 * I; p.K = H; p.total_rows = TK; p.gather_rows = T; p.b_rows_per_expert = 2 * I;
   p.off = expert_offset; p.gather = x_gather_idx;
+  p.gather_src = static_cast<const __nv_bfloat16*>(x); p.gather_ld = H;
   p.out0 = static_cast<__nv_bfloat16*>(z); p.ld0 = 2 * I;
   p.out1 = static_cast<__nv_bfloat16*>(y1); p.ld1 = I;
   p.status = status;
@@ -146,6 +183,7 @@ int smoe_down_projection_backward_act(const void* dout, const void* w2, const vo
   GemmParams p = {};
   p.E = E; p.N = I; p.K = H; p.total_rows = TK; p.gather_rows = T; p.b_rows_per_expert = H;
   p.off = expert_offset; p.gather = x_gather_idx; p.s_scatter = s_scatter_idx;
+  p.gather_src = static_cast<const __nv_bfloat16*>(dout); p.gather_ld = H;
   p.out0 = static_cast<__nv_bfloat16*>(dz); p.ld0 = 2 * I;
   p.out1 = static_cast<__nv_bfloat16*>(y1s); p.ld1 = I;
   p.z = static_cast<const __nv_bfloat16*>(z);
@@ -185,6 +223,7 @@ int smoe_down_projection_weight_grad(const void* dout, const void* y1s, void* dw
   GemmParams p = {};
   p.E = E; p.M = H; p.N = I; p.total_rows = TK; p.gather_rows = T;
   p.off = expert_offset; p.gather = x_gather_idx;
+  p.gather_src = static_cast<const __nv_bfloat16*>(dout); p.gather_ld = H;
   p.out0 = static_cast<__nv_bfloat16*>(dw2); p.ld0 = I; p.out0_expert_stride = (long long)H * I;
   p.status = status;
   return launch<true, true, true, false, true, EPI_STORE>(tmA, tmB, p, static_cast<cudaStream_t>(stream));
@@ -204,6 +243,7 @@ int smoe_up_projection_weight_grad(const void* x, const void* dz, void* dw1, con
   GemmParams p = {};
   p.E = E; p.M = 2 * I; p.N = H; p.total_rows = TK; p.gather_rows = T;
   p.off = expert_offset; p.gather = x_gather_idx;
+  p.gather_src = static_cast<const __nv_bfloat16*>(x); p.gather_ld = H;
   p.out0 = static_cast<__nv_bfloat16*>(dw1); p.ld0 = H; p.out0_expert_stride = (long long)2 * I * H;
   p.status = status;
   return launch<true, false, true, true, true, EPI_STORE>(tmA, tmB, p, static_cast<cudaStream_t>(stream));

@@ -1,8 +1,11 @@
 // Grouped (per-expert) GEMM for the MoE layer on sm_100a: TMA -> shared-memory ring -> tcgen05.mma with
 // the accumulator in tensor memory -> epilogue warps.  One persistent CTA per SM, three roles:
-//   warp 0      producer: TMA tiled loads and tile::gather4 row gathers into a 4-stage ring
+//   warp 0      producer: TMA tiled loads into a 4-stage ring (and, in the TMA-gather variant,
+//               tile::gather4 row gathers)
 //   warp 1      MMA issuer: owns tensor memory (2 accumulators of 128 x 256 fp32 = all 512 columns)
 //   warps 2..5  epilogue: tcgen05.ld the finished accumulator, apply the fused epilogue, store
+//   warps 6..9  (kernels with a gathered operand, LSU-gather variant) row gather with 16-byte
+//               cp.async copies written straight into the 128-byte-swizzled stage
 //
 // Two problem shapes share the kernel:
 //   ragged-M  out[off[e] + m, n] = sum_k A[row(off[e] + m), k] * B_e[n, k]       (forward, dH, dX)
@@ -24,7 +27,8 @@ constexpr int A_STAGE_BYTES = BM * BK * 2;  // 16 KiB
 constexpr int B_STAGE_BYTES = BN * BK * 2;  // 32 KiB
 constexpr int CHUNK_BYTES = BK * 128;       // one 64-element MN chunk of an MN-major tile: BK rows x 128 B
 constexpr int MAX_EXPERTS = 1024;
-constexpr int GEMM_THREADS = 192;
+constexpr int GEMM_THREADS = 192;          // warps 0..5
+constexpr int GATHER_THREADS = 128;        // warps 6..9 of the LSU-gather variant
 
 enum Epilogue : int {
   EPI_STORE = 0,    // out0[r, n] = bf16(acc)
@@ -46,6 +50,8 @@ struct GemmParams {
   int b_rows_per_expert;  // ragged-M: rows one expert occupies in B's flattened 2D tensor map
   const int* off;         // (E+1) first grouped row of every expert
   const int* gather;      // (total_rows) source row of every grouped row, or nullptr
+  const __nv_bfloat16* gather_src;  // the tensor the gather reads (LSU-gather variant)
+  long long gather_ld;              // its row pitch in elements
   __nv_bfloat16* out0;
   long long ld0;
   long long out0_expert_stride;  // ragged-K only
@@ -133,8 +139,8 @@ __device__ __forceinline__ bool decode_tile(const GemmParams& p, const SharedSto
   }
 }
 
-template <bool RAGGED_K, bool A_GATHER, bool A_MN, bool B_GATHER, bool B_MN, int EPI>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
+template <bool RAGGED_K, bool A_GATHER, bool A_MN, bool B_GATHER, bool B_MN, int EPI, bool LSU_GATHER>
+__global__ void __launch_bounds__((LSU_GATHER && (A_GATHER || B_GATHER)) ? GEMM_THREADS + GATHER_THREADS : GEMM_THREADS, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -147,11 +153,16 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   const int lane = threadIdx.x & 31;
   volatile int* abort_flag = &ss.abort_flag;
   const int num_n = (p.N + BN - 1) / BN;
+  constexpr bool kLsuA = LSU_GATHER && A_GATHER;   // A rows arrive through cp.async, not TMA
+  constexpr bool kLsuB = LSU_GATHER && B_GATHER;
+  constexpr bool kLsu = kLsuA || kLsuB;
+  static_assert(!(A_GATHER && B_GATHER), "at most one operand is gathered");
+  constexpr uint32_t kTmaBytes = (kLsuA ? 0 : A_STAGE_BYTES) + (kLsuB ? 0 : B_STAGE_BYTES);
 
   // ---- set-up -------------------------------------------------------------------------------
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(smem_u32(&ss.full[s]), 1);
+      mbar_init(smem_u32(&ss.full[s]), 1 + (kLsu ? GATHER_THREADS : 0));
       mbar_init(smem_u32(&ss.empty[s]), 1);
     }
     for (int a = 0; a < 2; ++a) {
@@ -203,7 +214,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     for (long long t = blockIdx.x; ok && decode_tile<RAGGED_K>(p, ss, t, num_n, tile); t += gridDim.x) {
       // ragged-M gathered A: the four source rows this lane fetches are the same for every k-block
       int ar[4] = {0, 0, 0, 0};
-      if constexpr (A_GATHER && !RAGGED_K) {
+      if constexpr (A_GATHER && !RAGGED_K && !kLsuA) {
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           const int r = tile.row0 + 4 * lane + j;
@@ -215,12 +226,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         const uint32_t bar = smem_u32(&ss.full[stage]);
         const uint32_t a_dst = smem_u32(sA + stage * A_STAGE_BYTES);
         const uint32_t b_dst = smem_u32(sB + stage * B_STAGE_BYTES);
-        if (lane == 0) mbar_arrive_expect_tx(bar, A_STAGE_BYTES + B_STAGE_BYTES);
+        if (lane == 0) mbar_arrive_expect_tx(bar, kTmaBytes);
         __syncwarp();
         const int k0 = RAGGED_K ? (tile.k_begin + kb * BK) : kb * BK;  // ragged-K: first grouped row of the stage
 
         // ---- A ----
-        if constexpr (!A_MN) {
+        if constexpr (kLsuA) {
+          // gathered by warps 6..9
+        } else if constexpr (!A_MN) {
           if constexpr (A_GATHER) {
             tma_gather4(&tmA, bar, a_dst + lane * 512, k0, ar[0], ar[1], ar[2], ar[3]);
           } else {
@@ -242,7 +255,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           }
         }
         // ---- B ----
-        if constexpr (!B_MN) {
+        if constexpr (kLsuB) {
+          // gathered by warps 6..9
+        } else if constexpr (!B_MN) {
           static_assert(!B_GATHER || B_MN, "a gathered B is only used MN-major");
           if (lane == 0) tma_load_2d(&tmB, bar, b_dst, k0, tile.e * p.b_rows_per_expert + tile.n0);
         } else {
@@ -291,6 +306,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         if (!mbar_wait(smem_u32(&ss.full[stage]), phase, abort_flag)) { ok = false; break; }
         tc_fence_after();
         if (lane == 0) {
+          if constexpr (kLsu) fence_proxy_async_smem();  // stage bytes written by cp.async -> async proxy reads
           const uint64_t a_desc = make_smem_desc(smem_u32(sA + stage * A_STAGE_BYTES), a_lbo, 1024);
           const uint64_t b_desc = make_smem_desc(smem_u32(sB + stage * B_STAGE_BYTES), b_lbo, 1024);
 #pragma unroll
@@ -309,6 +325,80 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
     }
     if (!ok && lane == 0 && p.status) atomicCAS(p.status, ST_OK, ST_TIMEOUT_MMA);
+  }
+  // ---- LSU gather producers ------------------------------------------------------------------
+  else if (warp >= 6) {
+    if constexpr (kLsu) {
+      const int gt = threadIdx.x - GEMM_THREADS;  // 0..127
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      Tile tile;
+      for (long long t = blockIdx.x; ok && decode_tile<RAGGED_K>(p, ss, t, num_n, tile); t += gridDim.x) {
+        if constexpr (!RAGGED_K) {
+          // K-major A tile: 128 rows x 128 B.  8 consecutive threads fetch the 8 16-byte pieces of a row;
+          // thread handles rows rb, rb+16, ...; the swizzle term (row & 7) is the same for all of them.
+          static_assert(kLsuA && !A_MN, "ragged-M kernels gather a K-major A");
+          const int c = gt & 7, rb = gt >> 3;
+          const uint32_t dst_off = rb * 128 + ((c ^ (rb & 7)) << 4);
+          const __nv_bfloat16* src[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int r = tile.row0 + rb + 16 * i;
+            const int idx = (r < p.total_rows) ? p.gather[r] : 0;
+            src[i] = p.gather_src + static_cast<long long>(idx) * p.gather_ld + c * 8;
+          }
+          for (int kb = 0; kb < tile.num_kb; ++kb) {
+            if (!mbar_wait(smem_u32(&ss.empty[stage]), phase ^ 1u, abort_flag)) { ok = false; break; }
+            const uint32_t dst = smem_u32(sA + stage * A_STAGE_BYTES) + dst_off;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) cp_async16(dst + i * 2048, src[i] + kb * BK, 16);
+            cp_async_arrive_noinc(smem_u32(&ss.full[stage]));
+            if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+          }
+        } else {
+          // MN-major tile: one reduction index (token) per 128-byte row, 64 tokens per chunk, one chunk
+          // per 64 elements of M (A: 2 chunks) or N (B: 4 chunks).  A token's elements are contiguous in
+          // global memory: CPR 16-byte pieces per token, fetched by CPR consecutive threads.
+          constexpr int CPR = kLsuA ? (BM / 8) : (BN / 8);           // 16 or 32 pieces per token
+          constexpr int ROWS_PER_PASS = GATHER_THREADS / CPR;          // 8 or 4 tokens per pass
+          constexpr int PASSES = BK / ROWS_PER_PASS;                   // 8 or 16
+          const int cc = gt % CPR, rb = gt / CPR;
+          const int chunk = cc >> 3, c = cc & 7;
+          const int col0 = (kLsuA ? tile.row0 : tile.n0) + cc * 8;
+          const bool col_ok = col0 < (kLsuA ? p.M : p.N);
+          const __nv_bfloat16* src_col = p.gather_src + col0;
+          uint8_t* stage_base = kLsuA ? sA : sB;
+          constexpr int STAGE_BYTES = kLsuA ? A_STAGE_BYTES : B_STAGE_BYTES;
+          int idx[PASSES];
+          auto load_idx = [&](int kb) {
+            const int k0 = tile.k_begin + kb * BK;
+#pragma unroll
+            for (int i = 0; i < PASSES; ++i) {
+              const int tok = k0 + rb + ROWS_PER_PASS * i;
+              idx[i] = (tok < tile.k_end && col_ok) ? p.gather[tok] : -1;
+            }
+          };
+          if (tile.num_kb > 0) load_idx(0);
+          for (int kb = 0; kb < tile.num_kb; ++kb) {
+            if (!mbar_wait(smem_u32(&ss.empty[stage]), phase ^ 1u, abort_flag)) { ok = false; break; }
+            const uint32_t dst = smem_u32(stage_base + stage * STAGE_BYTES) + chunk * CHUNK_BYTES;
+#pragma unroll
+            for (int i = 0; i < PASSES; ++i) {
+              const int r = rb + ROWS_PER_PASS * i;
+              const bool valid = idx[i] >= 0;
+              const __nv_bfloat16* src = src_col + static_cast<long long>(valid ? idx[i] : 0) * p.gather_ld;
+              cp_async16(dst + r * 128 + ((c ^ (r & 7)) << 4), src, valid ? 16u : 0u);
+            }
+            cp_async_arrive_noinc(smem_u32(&ss.full[stage]));
+            if (kb + 1 < tile.num_kb) load_idx(kb + 1);  // in flight while the next stage is awaited
+            if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+          }
+        }
+      }
+      cp_async_wait_all();
+      if (!ok && (gt & 31) == 0 && p.status) atomicCAS(p.status, ST_OK, ST_TIMEOUT_PRODUCER);
+    }
   }
   // ---- epilogue -----------------------------------------------------------------------------
   else {

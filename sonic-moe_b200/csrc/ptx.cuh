@@ -111,6 +111,21 @@ __device__ __forceinline__ void tma_gather4(const CUtensorMap* d, uint32_t bar, 
       : "memory");
 }
 
+// 16-byte asynchronous copy global -> shared through the LSU (bypasses L1); src_bytes == 0 writes zeros.
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+
+// Makes bar receive one arrival once every cp.async this thread has issued so far has landed.  The
+// arrival is counted in the barrier's expected count (.noinc).
+__device__ __forceinline__ void cp_async_arrive_noinc(uint32_t bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void cp_async_wait_all() {
+  asm volatile("cp.async.wait_all;" ::: "memory");
+}
+
 // ----------------------------------------------------------------------------------------------
 // tcgen05: tensor memory + 5th generation tensor-core MMA
 // ----------------------------------------------------------------------------------------------

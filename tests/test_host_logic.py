@@ -1,0 +1,100 @@
+"""Host-side logic that needs no GPU: module surface, state-dict layout, eager backend vs oracle, errors."""
+
+import pytest
+import torch
+
+from oracle import moe_oracle as orc
+
+
+def _module(E=8, K=2, H=128, I=64, seed=0):
+    import sonicmoe
+    from sonicmoe.enums import ActivationType
+
+    inp = orc.make_inputs(96, H, I, E, K, seed=seed)
+    m = sonicmoe.MoE(E, K, H, I, ActivationType.SWIGLU, False, 0.02)
+    with torch.no_grad():
+        m.router.weight.copy_(inp["router_w"])
+        m.c_fc.weight.copy_(inp["w1"])
+        m.c_proj.weight.copy_(inp["w2"])
+    return m, inp
+
+
+def test_public_surface(built_library):
+    import sonicmoe
+    from sonicmoe import KernelBackendMoE, MoE, count_cumsum, enable_quack_gemm, moe_TC_softmax_topk_layer  # noqa: F401
+    from sonicmoe.enums import ActivationType, is_glu
+    from sonicmoe.functional import count_cumsum as cc2, moe_general_routing_inputs  # noqa: F401
+
+    assert KernelBackendMoE("sonicmoe") is KernelBackendMoE.sonicmoe
+    assert ActivationType("swiglu") is ActivationType.SWIGLU
+    assert is_glu(ActivationType.GEGLU) and not is_glu(ActivationType.RELU_SQ)
+    with enable_quack_gemm(True):
+        pass
+
+
+def test_state_dict_layout(built_library):
+    m, _ = _module()
+    sd = m.state_dict()
+    assert set(sd) == {"router.weight", "c_fc.weight", "c_proj.weight"}
+    assert sd["router.weight"].shape == (8, 128)
+    assert sd["c_fc.weight"].shape == (8, 128, 128)   # (E, 2I, H)
+    assert sd["c_proj.weight"].shape == (8, 128, 64)  # (E, H, I)
+    import sonicmoe
+    from sonicmoe.enums import ActivationType
+
+    mb = sonicmoe.MoE(4, 2, 64, 64, ActivationType.GELU, True, 0.02)
+    assert mb.c_fc.weight.shape == (4, 64, 64) and mb.c_fc.bias.shape == (4, 64) and mb.c_proj.bias.shape == (4, 64)
+
+
+def test_eager_backend_matches_oracle(built_library):
+    from sonicmoe import KernelBackendMoE
+
+    m, inp = _module()
+    x = inp["x"].clone().requires_grad_(True)
+    o, aux = m(x.view(2, 48, 128), kernel_backend_moe=KernelBackendMoE.torch)
+    assert o.shape == (2, 48, 128)
+    grads = torch.autograd.grad(o, [x, m.router.weight, m.c_fc.weight, m.c_proj.weight], inp["dout"].view(2, 48, 128))
+    ref = orc.moe_layer(inp["x"], inp["router_w"], inp["w1"], inp["w2"], 2, dout=inp["dout"])
+    for got, want in zip((o.reshape(96, 128), aux, *grads),
+                         (ref["o"], ref["aux_loss"], ref["dx"], ref["drouter_w"], ref["dw1"], ref["dw2"])):
+        assert (got.detach() - want).norm() <= 2e-5 * want.norm()
+
+
+def test_cuda_backend_refuses_cpu_and_unsupported_inputs(built_library):
+    from sonicmoe import _lib
+    from sonicmoe.functional import moe_TC_softmax_topk_layer
+
+    m, inp = _module()
+    with pytest.raises(_lib.SonicMoEError):
+        m(inp["x"])  # CPU tensor: no fallback
+    w1 = m.c_fc.weight.permute(1, 2, 0)
+    w2 = m.c_proj.weight.permute(1, 2, 0)
+    with pytest.raises(AssertionError):
+        moe_TC_softmax_topk_layer(inp["x"], m.router.weight, w1, torch.zeros(8, 128), w2, None, 2)
+    with pytest.raises(NotImplementedError):
+        moe_TC_softmax_topk_layer(inp["x"], m.router.weight, w1, None, w2, None, 2, 0, "gelu")
+    with pytest.raises(ValueError):
+        m(inp["x"], kernel_backend_moe=__import__("sonicmoe").KernelBackendMoE.scattermoe)
+
+
+def test_rounded_counts():
+    from sonicmoe.functional.token_rounding import rounded_counts
+
+    f = torch.tensor([0, 1, 63, 64, 65, 127, 128, 191, 192, 193, 320, 448])
+    assert rounded_counts(f, "down").tolist() == [0, 0, 0, 0, 0, 0, 128, 128, 128, 128, 256, 384]
+    assert rounded_counts(f, "up").tolist() == [0, 128, 128, 128, 128, 128, 128, 256, 256, 256, 384, 512]
+    # nearest, exact halves go to the even multiple (64 -> 0, 192 -> 256, 320 -> 256, 448 -> 512)
+    assert rounded_counts(f, "nr").tolist() == [0, 0, 0, 0, 128, 128, 128, 128, 256, 256, 256, 512]
+    assert torch.equal(rounded_counts(f, "nr"), orc.rounded_counts(f, "nr"))
+
+
+def test_token_rounding_router_matches_oracle_on_cpu():
+    """The router is device-agnostic torch code; on CPU it must agree with the oracle bit for bit."""
+    from sonicmoe.functional.token_rounding import forward_token_choice_rounding
+
+    for dtype in (torch.float32, torch.bfloat16):
+        inp = orc.make_inputs(512, 64, 64, 8, 2, seed=11, dtype=dtype)
+        s, tok, exp = forward_token_choice_rounding(inp["x"], inp["router_w"], 8, 2, 128, "nr")
+        logits = torch.nn.functional.linear(inp["x"], inp["router_w"])
+        s_ref, tok_ref, exp_ref, _ = orc.token_rounding_route(logits, 2, "nr", dtype)
+        assert torch.equal(tok, tok_ref) and torch.equal(exp, exp_ref) and torch.equal(s, s_ref)

@@ -1,0 +1,210 @@
+"""Whole-layer parity on the GPU: the `sonicmoe.MoE` module and the functional entry points against the
+CPU oracle and against the golden fixtures produced by the reference.
+
+Tolerance: relative Frobenius error <= 1e-2 for every bf16 output and gradient (the bound stated for the
+bf16 layer); routing (indices, expert frequencies) bit-exact on the same logits.
+"""
+
+import pytest
+import torch
+
+from conftest import golden
+from oracle import moe_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+TOL = 1e-2
+
+
+def rel(a, b):
+    a = a.detach().float().cpu()
+    b = torch.as_tensor(b).float()
+    return ((a - b).norm() / (b.norm() + 1e-30)).item()
+
+
+def _module(T, H, I, E, K, seed, **kw):
+    import sonicmoe
+    from sonicmoe.enums import ActivationType
+
+    inp = orc.make_inputs(T, H, I, E, K, seed=seed, dtype=torch.bfloat16, **kw)
+    m = sonicmoe.MoE(E, K, H, I, ActivationType.SWIGLU, False, 0.02).cuda().to(torch.bfloat16)
+    with torch.no_grad():
+        m.router.weight.copy_(inp["router_w"])
+        m.c_fc.weight.copy_(inp["w1"])
+        m.c_proj.weight.copy_(inp["w2"])
+    return m, inp
+
+
+# reference test matrix shapes (tests/moe_test.py:25-38) scaled to sizes the CPU oracle finishes in seconds,
+# plus ragged / tiny / single-expert-per-token cases
+LAYER_SHAPES = [
+    (512, 256, 128, 16, 4),
+    (1024, 768, 256, 8, 2),
+    (777, 768, 320, 32, 8),
+    (640, 1536, 256, 64, 16),
+    (64, 128, 64, 4, 1),
+    (2048, 768, 256, 128, 8),
+    (30, 256, 64, 256, 8),   # far fewer tokens than experts: most experts are empty
+]
+
+
+@pytest.mark.parametrize("T,H,I,E,K", LAYER_SHAPES)
+@pytest.mark.parametrize("fused_combine", [False, True])
+def test_module_forward_backward_vs_oracle(built_library, T, H, I, E, K, fused_combine):
+    from sonicmoe import _lib, functional
+
+    m, inp = _module(T, H, I, E, K, seed=T + E)
+    prev = functional.set_fused_combine(fused_combine)
+    try:
+        x = inp["x"].cuda().requires_grad_(True)
+        o, aux = m(x.view(1, T, H))
+        assert o.shape == (1, T, H) and o.dtype == torch.bfloat16
+        grads = torch.autograd.grad(o, [x, m.router.weight, m.c_fc.weight, m.c_proj.weight],
+                                    inp["dout"].cuda().view(1, T, H))
+    finally:
+        functional.set_fused_combine(prev)
+    torch.cuda.synchronize()
+    _lib.check_status()
+
+    logits = torch.nn.functional.linear(x.detach(), m.router.weight.detach())
+    f32 = {k: v.float() for k, v in inp.items()}
+    ref = orc.moe_layer(f32["x"], f32["router_w"], f32["w1"], f32["w2"], K, dout=f32["dout"],
+                        logits=logits.float().cpu())
+    # routing on the same logits tensor is bit-exact
+    scores, idx = functional.topk_softmax(logits, K)
+    assert torch.equal(idx.cpu(), ref["indices"])
+    assert rel(o.view(T, H), ref["o"]) < TOL
+    assert rel(aux, ref["aux_loss"]) < 1e-3
+    # dx = expert path + router path; the router path is torch autograd on bf16 logits
+    assert rel(grads[0], ref["dx"]) < TOL
+    assert rel(grads[1], ref["drouter_w"]) < 2e-2  # dlogits are rounded to bf16 before the router GEMM
+    assert rel(grads[2], ref["dw1"]) < TOL
+    assert rel(grads[3], ref["dw2"]) < TOL
+    assert grads[2].shape == m.c_fc.weight.shape and grads[3].shape == m.c_proj.weight.shape
+
+
+@pytest.mark.parametrize("name", ["layer_small", "layer_ties", "layer_k1"])
+def test_functional_layer_vs_reference_golden(built_library, name):
+    """The device path against outputs of the reference's own eager layer (fp32 router, bf16 experts)."""
+    from sonicmoe import _lib
+    from sonicmoe.functional import moe_TC_softmax_topk_layer
+
+    g = golden(name)
+    T, H, I, E, K, seed, _ = [int(v) for v in g["meta"]]
+    inp = orc.make_inputs(T, H, I, E, K, seed=seed, dtype=torch.bfloat16)
+    x = inp["x"].cuda().requires_grad_(True)
+    rw = inp["router_w"].float().cuda().requires_grad_(True)  # fp32 router: same logits as the reference run
+    w1 = inp["w1"].cuda().requires_grad_(True)
+    w2 = inp["w2"].cuda().requires_grad_(True)
+    o, logits, freq = moe_TC_softmax_topk_layer(x, rw, w1.permute(1, 2, 0), None, w2.permute(1, 2, 0), None, K)
+    grads = torch.autograd.grad(o, [x, rw, w1, w2], inp["dout"].cuda())
+    torch.cuda.synchronize()
+    _lib.check_status()
+    assert torch.equal(freq.cpu(), torch.from_numpy(g["expert_frequency"]))
+    assert rel(logits, g["logits"]) < 1e-5
+    assert rel(o, g["o"]) < TOL
+    for got, key in zip(grads, ("dx", "drouter_w", "dw1", "dw2")):
+        assert rel(got, g[key]) < TOL, key
+
+
+def test_inference_mode_matches_training_forward(built_library):
+    m, inp = _module(512, 256, 128, 16, 4, seed=3)
+    x = inp["x"].cuda()
+    o_train, _ = m(x)
+    m.eval()
+    with torch.no_grad():
+        o_eval, _ = m(x)
+    o_flag, _ = m.train()(x, is_inference_mode=True)
+    assert torch.equal(o_train, o_eval) and torch.equal(o_train, o_flag)
+
+
+@pytest.mark.parametrize("routing", ["nr", "up", "down"])
+@pytest.mark.parametrize("T,H,I,E,K", [(1024, 256, 128, 8, 2), (2048, 512, 128, 16, 4)])
+def test_token_rounding_layer_vs_oracle(built_library, routing, T, H, I, E, K):
+    """Token-rounding router + general-routing layer: selections bit-exact, outputs and gradients in tolerance."""
+    from sonicmoe import _lib
+    from sonicmoe.functional import forward_token_choice_rounding, moe_general_routing_inputs
+
+    inp = orc.make_inputs(T, H, I, E, K, seed=T + E + len(routing), dtype=torch.bfloat16)
+    x = inp["x"].cuda().requires_grad_(True)
+    w1 = inp["w1"].cuda().requires_grad_(True)
+    w2 = inp["w2"].cuda().requires_grad_(True)
+    scores, tokens, experts = forward_token_choice_rounding(x.detach(), inp["router_w"].cuda(), E, K, 128, routing)
+    logits = torch.nn.functional.linear(x.detach(), inp["router_w"].cuda())
+    s_ref, t_ref, e_ref, _ = orc.token_rounding_route(logits.cpu(), K, routing, torch.bfloat16)
+    assert torch.equal(tokens.cpu(), t_ref) and torch.equal(experts.cpu(), e_ref)
+    assert torch.equal(scores.cpu(), s_ref)
+    counts = torch.bincount(experts.long(), minlength=E)
+    assert (counts % 128 == 0).all()
+
+    sc = scores.detach().clone().requires_grad_(True)
+    o, freq = moe_general_routing_inputs(x, sc, tokens, experts, w1.permute(1, 2, 0), None, w2.permute(1, 2, 0),
+                                         None, E, 0, __import__("sonicmoe").ActivationType.SWIGLU)
+    grads = torch.autograd.grad(o, [x, w1, w2, sc], inp["dout"].cuda())
+    torch.cuda.synchronize()
+    _lib.check_status()
+    assert torch.equal(freq.cpu(), counts.cpu().int())
+    f32 = {k: v.float() for k, v in inp.items()}
+    ref = orc.general_routing_layer(f32["x"], f32["w1"], f32["w2"], s_ref.float(), t_ref, e_ref, dout=f32["dout"])
+    assert rel(o, ref["o"]) < TOL
+    assert rel(grads[0], ref["dx"]) < TOL
+    assert rel(grads[1], ref["dw1"]) < TOL
+    assert rel(grads[2], ref["dw2"]) < TOL
+    assert grads[3].dtype == torch.bfloat16 and rel(grads[3], ref["ds"]) < TOL
+
+
+def test_general_routing_with_empty_tokens_and_experts(built_library):
+    from sonicmoe import ActivationType, _lib
+    from sonicmoe.functional import moe_general_routing_inputs
+
+    T, H, I, E = 200, 128, 64, 8
+    inp = orc.make_inputs(T, H, I, E, 2, seed=5, dtype=torch.bfloat16, w_std=0.05)
+    g = torch.Generator().manual_seed(1)
+    n = 300
+    tokens = torch.randint(0, T // 2, (n,), generator=g).sort().values.int()  # upper half of the tokens unused
+    experts = torch.randint(0, E - 2, (n,), generator=g).int()                # two experts unused
+    scores = torch.rand(n, generator=g)
+    x = inp["x"].cuda().requires_grad_(True)
+    w1 = inp["w1"].cuda().requires_grad_(True)
+    w2 = inp["w2"].cuda().requires_grad_(True)
+    sc = scores.cuda().requires_grad_(True)
+    o, freq = moe_general_routing_inputs(x, sc, tokens.cuda(), experts.cuda(), w1.permute(1, 2, 0), None,
+                                         w2.permute(1, 2, 0), None, E, 0, ActivationType.SWIGLU)
+    grads = torch.autograd.grad(o, [x, w1, w2, sc], inp["dout"].cuda())
+    torch.cuda.synchronize()
+    _lib.check_status()
+    f32 = {k: v.float() for k, v in inp.items()}
+    ref = orc.general_routing_layer(f32["x"], f32["w1"], f32["w2"], scores, tokens, experts, dout=f32["dout"])
+    assert (o[T // 2:] == 0).all() and (grads[0][T // 2:] == 0).all()
+    assert (grads[1][E - 2:] == 0).all() and (grads[2][E - 2:] == 0).all()
+    assert rel(o, ref["o"]) < TOL and rel(grads[0], ref["dx"]) < TOL
+    assert rel(grads[1], ref["dw1"]) < TOL and rel(grads[2], ref["dw2"]) < TOL
+    assert grads[3].dtype == torch.float32 and rel(grads[3], ref["ds"]) < 1e-2
+
+
+def test_linearity_at_full_hidden_size(built_library):
+    """Size-independent property at the benchmark's H and I: with the routing fixed, the layer output is linear in
+    the routing scores, o(a*s1 + b*s2) = a*o(s1) + b*o(s2), and doubling dout doubles every gradient."""
+    from sonicmoe import ActivationType, _lib
+    from sonicmoe.functional import moe_general_routing_inputs
+
+    T, H, I, E, K = 4096, 4096, 1024, 16, 2
+    inp = orc.make_inputs(T, H, I, E, K, seed=1, dtype=torch.bfloat16)
+    g = torch.Generator().manual_seed(2)
+    experts = torch.stack([torch.randperm(E, generator=g)[:K] for _ in range(T)]).reshape(-1).int().cuda()
+    tokens = torch.arange(T).repeat_interleave(K).int().cuda()
+    s1 = torch.rand(T * K, generator=g).cuda()
+    s2 = torch.rand(T * K, generator=g).cuda()
+    x = inp["x"].cuda()
+    w1 = inp["w1"].cuda().permute(1, 2, 0)
+    w2 = inp["w2"].cuda().permute(1, 2, 0)
+
+    def run(s):
+        with torch.no_grad():
+            return moe_general_routing_inputs(x, s, tokens, experts, w1, None, w2, None, E, 0,
+                                              ActivationType.SWIGLU)[0].float()
+
+    o1, o2, o12 = run(s1), run(s2), run(0.5 * s1 + 2.0 * s2)
+    assert ((o12 - (0.5 * o1 + 2.0 * o2)).norm() / o12.norm()).item() < TOL
+    torch.cuda.synchronize()
+    _lib.check_status()
