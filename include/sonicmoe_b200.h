@@ -34,7 +34,8 @@ enum {
   SMOE_ERR_TENSORMAP = -4, /* the driver rejected a TMA descriptor */
   SMOE_ERR_LAUNCH = -5,    /* the kernel launch itself failed */
   SMOE_ERR_DTYPE = -6,     /* unknown dtype code */
-  SMOE_ERR_WORKSPACE = -7  /* workspace missing or too small */
+  SMOE_ERR_WORKSPACE = -7, /* workspace missing or too small */
+  SMOE_ERR_NOALLOC_LIMIT = -8 /* size exceeds what the allocation-free entry point's built-in scratch holds */
 };
 
 enum { SMOE_ST_OK = 0, SMOE_ST_TIMEOUT_PRODUCER = 1, SMOE_ST_TIMEOUT_MMA = 2, SMOE_ST_TIMEOUT_EPILOGUE = 3 };
@@ -70,6 +71,18 @@ int smoe_softmax_topk_backward(void* dlogits, int dlogits_dtype, const float* ds
 size_t smoe_count_cumsum_workspace_bytes(int E);
 int smoe_count_cumsum(const void* x, int x_dtype, long long n, int E, int* count, int* cumsum, void* workspace,
                       void* stream);
+
+/* Allocation-free form of smoe_count_cumsum (same arguments minus the workspace, same results).  It has no
+ * counterpart in the reference.  It exists for hosts that can hand this library nothing but the input and
+ * output buffers: a runtime whose device memory is planned ahead of time and owns the only allocator, or a call
+ * site where cudaMalloc's implicit device-wide synchronisation cannot be tolerated.  The scratch is a 512 KiB
+ * array compiled into the library (held by every GPU that loads it), which limits E to
+ * smoe_count_cumsum_noalloc_max_experts() = 1024; a larger E returns SMOE_ERR_NOALLOC_LIMIT.  The first call on
+ * a device resolves the array's address and should happen before any stream capture.  Calls on one device share
+ * the array: they must not overlap on the GPU (issue them on one stream, or order the streams). */
+int smoe_count_cumsum_noalloc_max_experts(void);
+int smoe_count_cumsum_noalloc(const void* x, int x_dtype, long long n, int E, int* count, int* cumsum,
+                              void* stream);
 
 /* From the flat expert id of each of n routed pairs: expert_count (E), expert_offset (E+1, leading 0),
  * and a stable counting sort by expert: s_scatter_idx[r] = flat slot of grouped row r,

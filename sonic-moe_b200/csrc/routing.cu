@@ -7,6 +7,8 @@
 #include <math.h>
 #include <stdint.h>
 
+#include <mutex>
+
 #include "../../include/sonicmoe_b200.h"
 
 namespace smoe {
@@ -402,6 +404,29 @@ __global__ void __launch_bounds__(256) ds_reduce_kernel(const float* __restrict_
   ds[s_scatter[r]] = static_cast<OutT>(acc);
 }
 
+// Scratch of the allocation-free entry point: kMaxSortBlocks x kNoAllocMaxExperts per-chunk bins
+// (512 KiB), resident on every GPU that loads the library until the process exits.
+constexpr int kNoAllocMaxExperts = 1024;
+constexpr int kMaxDevices = 64;
+static __device__ __align__(256) int g_noalloc_hist[kMaxSortBlocks * kNoAllocMaxExperts];
+
+// Device address of g_noalloc_hist on the current device.  In host code the symbol itself is only a
+// host-side handle, never a device pointer, so the address is looked up once per device.
+static int noalloc_scratch(int** out) {
+  static std::mutex mu;
+  static int* cached[kMaxDevices] = {};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return SMOE_ERR_DRIVER;
+  std::lock_guard<std::mutex> lock(mu);
+  if (cached[dev] == nullptr) {
+    void* ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_noalloc_hist) != cudaSuccess || ptr == nullptr) return SMOE_ERR_DRIVER;
+    cached[dev] = static_cast<int*>(ptr);
+  }
+  *out = cached[dev];
+  return SMOE_OK;
+}
+
 static int sort_blocks(long long n) {
   long long b = (n + 4 * kSortThreads - 1) / (4 * kSortThreads);
   if (b < 1) b = 1;
@@ -475,6 +500,37 @@ int smoe_count_cumsum(const void* x, int x_dtype, long long n, int E, int* count
 }
 
 size_t smoe_route_metadata_workspace_bytes(int E) { return smoe_count_cumsum_workspace_bytes(E); }
+
+int smoe_count_cumsum_noalloc_max_experts(void) { return kNoAllocMaxExperts; }
+
+// Same result as smoe_count_cumsum, for hosts that can give the library no workspace: the per-chunk
+// histograms live in the file-scope device array g_noalloc_hist instead.  Nothing is allocated or freed
+// here, and no allocating runtime or library routine is called.
+//   * E is limited to kNoAllocMaxExperts (1024) bins; a larger E returns SMOE_ERR_NOALLOC_LIMIT.
+//   * The first call on each device looks the array's device address up (cudaGetSymbolAddress, with that
+//     device current) and caches it; make that first call before any stream capture begins.
+//   * All calls on a device share the one array.  It keeps whatever the previous call left in it, which is
+//     harmless: the histogram kernel stores every entry the scan kernel later reads, so nothing has to
+//     start at zero.  Two calls whose kernels overlap on the GPU (different streams) race on it: keep calls
+//     on one device stream-ordered with respect to each other.
+int smoe_count_cumsum_noalloc(const void* x, int x_dtype, long long n, int E, int* count, int* cumsum,
+                              void* stream) {
+  if (n < 0 || E <= 0 || count == nullptr) return SMOE_ERR_SHAPE;
+  if (E > kNoAllocMaxExperts) return SMOE_ERR_NOALLOC_LIMIT;
+  if (x_dtype != SMOE_I32 && x_dtype != SMOE_I64) return SMOE_ERR_DTYPE;
+  int* hist = nullptr;
+  const int rc = noalloc_scratch(&hist);
+  if (rc != SMOE_OK) return rc;
+  cudaStream_t st = S(stream);
+  const int blocks = sort_blocks(n);
+  if (x_dtype == SMOE_I32)
+    chunk_histogram_kernel<int><<<blocks, kSortThreads, E * sizeof(int), st>>>(static_cast<const int*>(x), n, E, hist);
+  else
+    chunk_histogram_kernel<long long><<<blocks, kSortThreads, E * sizeof(int), st>>>(
+        static_cast<const long long*>(x), n, E, hist);
+  scan_bins_kernel<<<1, 1024, 0, st>>>(hist, blocks, E, nullptr, count, cumsum, nullptr);
+  return launch_rc();
+}
 
 int smoe_route_metadata(const int* expert_idx, const int* token_idx, long long n, int E, int K, int* expert_count,
                         int* expert_offset, int* s_scatter_idx, int* s_reverse_scatter_idx, int* x_gather_idx,

@@ -25,6 +25,7 @@ _ERRORS = {
     -5: "kernel launch failed",
     -6: "unknown dtype code",
     -7: "workspace missing or too small",
+    -8: "size exceeds the built-in scratch of the allocation-free entry point",
 }
 
 P, I, LL = c_void_p, c_int, c_longlong
@@ -36,6 +37,8 @@ SIGNATURES: dict[str, tuple] = {
     "smoe_softmax_topk_backward": (I, [P, I, P, P, P, I, I, I, P]),
     "smoe_count_cumsum_workspace_bytes": (c_size_t, [I]),
     "smoe_count_cumsum": (I, [P, I, LL, I, P, P, P, P]),
+    "smoe_count_cumsum_noalloc_max_experts": (I, []),
+    "smoe_count_cumsum_noalloc": (I, [P, I, LL, I, P, P, P]),
     "smoe_route_metadata_workspace_bytes": (c_size_t, [I]),
     "smoe_route_metadata": (I, [P, P, LL, I, I, P, P, P, P, P, P, P]),
     "smoe_sorted_offsets": (I, [P, LL, I, P, P]),
