@@ -188,7 +188,7 @@ def zero_grads(moe, x):
         p.grad = None
 
 
-def time_kernels(moe, x, dout, cfg, peaks):
+def time_kernels(moe, x, dout, cfg, peaks, reps=5):
     """CUDA-event time of each grouped GEMM launched alone on the benchmark's tensors (inputs far larger than
     L2), and of the two gather-sum reductions; returns per-kernel figures and the dominant GEMM."""
     from sonicmoe import _lib, functional as fn
@@ -237,7 +237,6 @@ def time_kernels(moe, x, dout, cfg, peaks):
             y2.data_ptr(), o.data_ptr(), None, 0, rev, None, T, H, K, stream)),
     }
     out = {}
-    reps = 5
 
     def timed(fn_):
         fn_()  # warm
@@ -403,6 +402,11 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    # profiling aid: time (or let ncu capture) each kernel alone on a reduced token / expert count
+    ap.add_argument("--kernels-only", action="store_true")
+    ap.add_argument("--tokens", type=int, default=CFG["T"])
+    ap.add_argument("--experts", type=int, default=CFG["E"])
+    ap.add_argument("--reps", type=int, default=5)
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -412,6 +416,17 @@ def main():
         return
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the layer has no CPU path (use --impl reference for the CPU arm)")
+    if args.kernels_only:
+        cfg = dict(CFG, T=args.tokens, E=args.experts)
+        dev = torch.device("cuda", local_rank)
+        torch.cuda.set_device(dev)
+        moe = build_layer(cfg, dev)
+        g = torch.Generator(device=dev).manual_seed(1)
+        x = torch.randn(cfg["T"], cfg["H"], generator=g, device=dev).bfloat16()
+        dout = torch.randn(cfg["T"], cfg["H"], generator=g, device=dev).bfloat16()
+        kernels, dominant, _ = time_kernels(moe, x, dout, cfg, load_peaks(), reps=args.reps)
+        print(json.dumps({"config": cfg, "kernels": kernels, "dominant": dominant}), flush=True)
+        return
     run_gpu_arm(args, rank, world, local_rank)
 
 

@@ -70,18 +70,20 @@ static int num_sms() {
 }
 
 // Gathered operands are fetched by cp.async warps (default) or, with SMOE_TMA_GATHER=1 in the
-// environment, by TMA tile::gather4 from the producer warp.
+// environment, by TMA tile::gather4 from the producer warp.  SMOE_EPI_WARPS (4|8) and
+// SMOE_GATHER_WARPS (4|8) override the per-kernel warp counts (for tuning runs).
+static int env_int(const char* name, int dflt) {
+  const char* e = getenv(name);
+  return (e != nullptr && e[0] != 0) ? atoi(e) : dflt;
+}
 static bool use_tma_gather() {
-  static const bool v = [] {
-    const char* e = getenv("SMOE_TMA_GATHER");
-    return e != nullptr && e[0] == '1';
-  }();
+  static const bool v = env_int("SMOE_TMA_GATHER", 0) == 1;
   return v;
 }
 
-template <bool RAGGED_K, bool A_GATHER, bool A_MN, bool B_GATHER, bool B_MN, int EPI, bool LSU_GATHER>
+template <bool RAGGED_K, bool A_GATHER, bool A_MN, bool B_GATHER, bool B_MN, int EPI, int EW, int GW>
 static int launch_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, cudaStream_t stream) {
-  auto kernel = grouped_gemm_kernel<RAGGED_K, A_GATHER, A_MN, B_GATHER, B_MN, EPI, LSU_GATHER>;
+  auto kernel = grouped_gemm_kernel<RAGGED_K, A_GATHER, A_MN, B_GATHER, B_MN, EPI, EW, GW>;
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_BYTES) != cudaSuccess)
@@ -90,19 +92,32 @@ static int launch_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const 
   }
   const int sms = num_sms();
   if (sms <= 0) return SMOE_ERR_DRIVER;
-  constexpr int threads = (LSU_GATHER && (A_GATHER || B_GATHER)) ? GEMM_THREADS + GATHER_THREADS : GEMM_THREADS;
-  kernel<<<sms, threads, GEMM_SMEM_BYTES, stream>>>(tmA, tmB, p);
+  kernel<<<sms, gemm_threads(EW, GW), GEMM_SMEM_BYTES, stream>>>(tmA, tmB, p);
   return cudaGetLastError() == cudaSuccess ? SMOE_OK : SMOE_ERR_LAUNCH;
 }
 
+// dflt_ew / dflt_gw: the tuned warp counts of the calling entry point.
 template <bool RAGGED_K, bool A_GATHER, bool A_MN, bool B_GATHER, bool B_MN, int EPI>
-static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, cudaStream_t stream) {
-  if constexpr (A_GATHER || B_GATHER) {
-    if (use_tma_gather()) return launch_variant<RAGGED_K, A_GATHER, A_MN, B_GATHER, B_MN, EPI, false>(tmA, tmB, p, stream);
-    return launch_variant<RAGGED_K, A_GATHER, A_MN, B_GATHER, B_MN, EPI, true>(tmA, tmB, p, stream);
-  } else {
-    return launch_variant<RAGGED_K, A_GATHER, A_MN, B_GATHER, B_MN, EPI, false>(tmA, tmB, p, stream);
+static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, cudaStream_t stream,
+                  int dflt_ew, int dflt_gw) {
+  static const int env_ew = env_int("SMOE_EPI_WARPS", 0);
+  static const int env_gw = env_int("SMOE_GATHER_WARPS", 0);
+  const int ew = (env_ew == 4 || env_ew == 8) ? env_ew : dflt_ew;
+  int gw = (env_gw == 4 || env_gw == 8) ? env_gw : dflt_gw;
+  constexpr bool kGather = A_GATHER || B_GATHER;
+  if (!kGather || use_tma_gather()) gw = 0;
+#define SMOE_LAUNCH(EW_, GW_) \
+  return launch_variant<RAGGED_K, A_GATHER, A_MN, B_GATHER, B_MN, EPI, EW_, GW_>(tmA, tmB, p, stream)
+  if (ew == 4 && gw == 0) SMOE_LAUNCH(4, 0);
+  if (ew == 8 && gw == 0) SMOE_LAUNCH(8, 0);
+  if constexpr (kGather) {
+    if (ew == 4 && gw == 4) SMOE_LAUNCH(4, 4);
+    if (ew == 4 && gw == 8) SMOE_LAUNCH(4, 8);
+    if (ew == 8 && gw == 4) SMOE_LAUNCH(8, 4);
+    if (ew == 8 && gw == 8) SMOE_LAUNCH(8, 8);
   }
+#undef SMOE_LAUNCH
+  return SMOE_ERR_SHAPE;
 }
 
 static bool bad_shape(int H, int I, int E) {
@@ -136,7 +151,7 @@ int smoe_up_projection_forward(const void* x, const void* w1, void* z, void* y1,
   p.out0 = static_cast<__nv_bfloat16*>(z); p.ld0 = 2 * I;
   p.out1 = static_cast<__nv_bfloat16*>(y1); p.ld1 = I;
   p.status = status;
-  return launch<false, true, false, false, false, EPI_SWIGLU>(tmA, tmB, p, static_cast<cudaStream_t>(stream));
+  return launch<false, true, false, false, false, EPI_SWIGLU>(tmA, tmB, p, static_cast<cudaStream_t>(stream), 4, 4);
 }
 
 int smoe_down_projection_forward(const void* y1, const void* w2, void* y2, const int* expert_offset, int H, int I,
@@ -151,7 +166,7 @@ int smoe_down_projection_forward(const void* y1, const void* w2, void* y2, const
   p.off = expert_offset;
   p.out0 = static_cast<__nv_bfloat16*>(y2); p.ld0 = H;
   p.status = status;
-  return launch<false, false, false, false, false, EPI_STORE>(tmA, tmB, p, static_cast<cudaStream_t>(stream));
+  return launch<false, false, false, false, false, EPI_STORE>(tmA, tmB, p, static_cast<cudaStream_t>(stream), 4, 0);
 }
 
 int smoe_down_projection_forward_scatter(const void* y1, const void* w2, float* o_acc, const void* scores,
@@ -168,7 +183,7 @@ int smoe_down_projection_forward_scatter(const void* y1, const void* w2, float* 
   p.off = expert_offset; p.gather = x_gather_idx; p.s_scatter = s_scatter_idx;
   p.scores = scores; p.scores_are_bf16 = scores_are_bf16; p.acc_out = o_acc;
   p.status = status;
-  return launch<false, false, false, false, false, EPI_SCATTER>(tmA, tmB, p, static_cast<cudaStream_t>(stream));
+  return launch<false, false, false, false, false, EPI_SCATTER>(tmA, tmB, p, static_cast<cudaStream_t>(stream), 4, 0);
 }
 
 int smoe_down_projection_backward_act(const void* dout, const void* w2, const void* z, const void* scores,
@@ -189,10 +204,10 @@ int smoe_down_projection_backward_act(const void* dout, const void* w2, const vo
   p.z = static_cast<const __nv_bfloat16*>(z);
   p.scores = scores; p.scores_are_bf16 = scores_are_bf16; p.ds_partial = ds_partial;
   p.status = status;
-  return launch<false, true, false, false, true, EPI_DSWIGLU>(tmA, tmB, p, static_cast<cudaStream_t>(stream));
+  return launch<false, true, false, false, true, EPI_DSWIGLU>(tmA, tmB, p, static_cast<cudaStream_t>(stream), 4, 4);
 }
 
-int smoe_ds_partial_columns(int I) { return (I + BN - 1) / BN; }
+int smoe_ds_partial_columns(int I) { return 2 * ((I + BN - 1) / BN); }
 
 int smoe_up_projection_backward_dx(const void* dz, const void* w1, void* dx_expanded, const int* expert_offset, int H,
                                    int I, int E, int TK, int* status, void* stream) {
@@ -206,7 +221,7 @@ int smoe_up_projection_backward_dx(const void* dz, const void* w1, void* dx_expa
   p.off = expert_offset;
   p.out0 = static_cast<__nv_bfloat16*>(dx_expanded); p.ld0 = H;
   p.status = status;
-  return launch<false, false, false, false, true, EPI_STORE>(tmA, tmB, p, static_cast<cudaStream_t>(stream));
+  return launch<false, false, false, false, true, EPI_STORE>(tmA, tmB, p, static_cast<cudaStream_t>(stream), 4, 0);
 }
 
 int smoe_down_projection_weight_grad(const void* dout, const void* y1s, void* dw2, const int* expert_offset,
@@ -226,7 +241,7 @@ int smoe_down_projection_weight_grad(const void* dout, const void* y1s, void* dw
   p.gather_src = static_cast<const __nv_bfloat16*>(dout); p.gather_ld = H;
   p.out0 = static_cast<__nv_bfloat16*>(dw2); p.ld0 = I; p.out0_expert_stride = (long long)H * I;
   p.status = status;
-  return launch<true, true, true, false, true, EPI_STORE>(tmA, tmB, p, static_cast<cudaStream_t>(stream));
+  return launch<true, true, true, false, true, EPI_STORE>(tmA, tmB, p, static_cast<cudaStream_t>(stream), 8, 8);
 }
 
 int smoe_up_projection_weight_grad(const void* x, const void* dz, void* dw1, const int* expert_offset,
@@ -246,7 +261,7 @@ int smoe_up_projection_weight_grad(const void* x, const void* dz, void* dw1, con
   p.gather_src = static_cast<const __nv_bfloat16*>(x); p.gather_ld = H;
   p.out0 = static_cast<__nv_bfloat16*>(dw1); p.ld0 = H; p.out0_expert_stride = (long long)2 * I * H;
   p.status = status;
-  return launch<true, false, true, true, true, EPI_STORE>(tmA, tmB, p, static_cast<cudaStream_t>(stream));
+  return launch<true, false, true, true, true, EPI_STORE>(tmA, tmB, p, static_cast<cudaStream_t>(stream), 8, 8);
 }
 
 }  // extern "C"

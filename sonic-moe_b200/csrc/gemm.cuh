@@ -27,8 +27,11 @@ constexpr int A_STAGE_BYTES = BM * BK * 2;  // 16 KiB
 constexpr int B_STAGE_BYTES = BN * BK * 2;  // 32 KiB
 constexpr int CHUNK_BYTES = BK * 128;       // one 64-element MN chunk of an MN-major tile: BK rows x 128 B
 constexpr int MAX_EXPERTS = 1024;
-constexpr int GEMM_THREADS = 192;          // warps 0..5
-constexpr int GATHER_THREADS = 128;        // warps 6..9 of the LSU-gather variant
+// Warp roles: warp 0 TMA producer, warp 1 MMA issuer, then EW epilogue warps (4 or 8), then GW
+// cp.async gather warps (0, 4 or 8).
+__host__ __device__ constexpr int gemm_threads(int epi_warps, int gather_warps) {
+  return 32 * (2 + epi_warps + gather_warps);
+}
 
 enum Epilogue : int {
   EPI_STORE = 0,    // out0[r, n] = bf16(acc)
@@ -62,7 +65,7 @@ struct GemmParams {
   const void* scores;       // flat routing scores, fp32 or bf16
   int scores_are_bf16;
   const int* s_scatter;     // (total_rows) flat score slot of every grouped row
-  float* ds_partial;        // (ceil(N/BN), total_rows) fp32
+  float* ds_partial;        // (2 * ceil(N/BN), total_rows) fp32: one row of partials per 128 accumulator columns
   float* acc_out;           // EPI_SCATTER: (gather_rows, N) fp32
   int* status;              // device word, 0 = ok
 };
@@ -139,8 +142,8 @@ __device__ __forceinline__ bool decode_tile(const GemmParams& p, const SharedSto
   }
 }
 
-template <bool RAGGED_K, bool A_GATHER, bool A_MN, bool B_GATHER, bool B_MN, int EPI, bool LSU_GATHER>
-__global__ void __launch_bounds__((LSU_GATHER && (A_GATHER || B_GATHER)) ? GEMM_THREADS + GATHER_THREADS : GEMM_THREADS, 1)
+template <bool RAGGED_K, bool A_GATHER, bool A_MN, bool B_GATHER, bool B_MN, int EPI, int EW, int GW>
+__global__ void __launch_bounds__(gemm_threads(EW, GW), 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -153,6 +156,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   const int lane = threadIdx.x & 31;
   volatile int* abort_flag = &ss.abort_flag;
   const int num_n = (p.N + BN - 1) / BN;
+  constexpr bool LSU_GATHER = GW > 0;
+  constexpr int GATHER_THREADS = 32 * GW;
+  constexpr int FIRST_GATHER_WARP = 2 + EW;
+  static_assert(EW == 4 || EW == 8, "4 or 8 epilogue warps");
+  static_assert(GW == 0 || GW == 4 || GW == 8, "0, 4 or 8 gather warps");
   constexpr bool kLsuA = LSU_GATHER && A_GATHER;   // A rows arrive through cp.async, not TMA
   constexpr bool kLsuB = LSU_GATHER && B_GATHER;
   constexpr bool kLsu = kLsuA || kLsuB;
@@ -167,7 +175,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(smem_u32(&ss.acc_full[a]), 1);
-      mbar_init(smem_u32(&ss.acc_empty[a]), 4);  // one arrival per epilogue warp
+      mbar_init(smem_u32(&ss.acc_empty[a]), EW);  // one arrival per epilogue warp
     }
     ss.abort_flag = 0;
     fence_mbar_init();
@@ -222,7 +230,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         }
       }
       for (int kb = 0; kb < tile.num_kb; ++kb) {
-        if (!mbar_wait(smem_u32(&ss.empty[stage]), phase ^ 1u, abort_flag)) { ok = false; break; }
+        if (!mbar_wait_warp(smem_u32(&ss.empty[stage]), phase ^ 1u, abort_flag)) { ok = false; break; }
         const uint32_t bar = smem_u32(&ss.full[stage]);
         const uint32_t a_dst = smem_u32(sA + stage * A_STAGE_BYTES);
         const uint32_t b_dst = smem_u32(sB + stage * B_STAGE_BYTES);
@@ -299,11 +307,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     Tile tile;
     for (long long t = blockIdx.x; ok && decode_tile<RAGGED_K>(p, ss, t, num_n, tile); t += gridDim.x) {
       if (tile.num_kb == 0) continue;  // empty expert: the epilogue writes zeros without an accumulator
-      if (!mbar_wait(smem_u32(&ss.acc_empty[acc]), acc_phase ^ 1u, abort_flag)) { ok = false; break; }
+      if (!mbar_wait_warp(smem_u32(&ss.acc_empty[acc]), acc_phase ^ 1u, abort_flag)) { ok = false; break; }
       tc_fence_after();
       const uint32_t d_tmem = tmem_base + acc * BN;
       for (int kb = 0; kb < tile.num_kb; ++kb) {
-        if (!mbar_wait(smem_u32(&ss.full[stage]), phase, abort_flag)) { ok = false; break; }
+        if (!mbar_wait_warp(smem_u32(&ss.full[stage]), phase, abort_flag)) { ok = false; break; }
         tc_fence_after();
         if (lane == 0) {
           if constexpr (kLsu) fence_proxy_async_smem();  // stage bytes written by cp.async -> async proxy reads
@@ -327,9 +335,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     if (!ok && lane == 0 && p.status) atomicCAS(p.status, ST_OK, ST_TIMEOUT_MMA);
   }
   // ---- LSU gather producers ------------------------------------------------------------------
-  else if (warp >= 6) {
+  else if (warp >= FIRST_GATHER_WARP) {
     if constexpr (kLsu) {
-      const int gt = threadIdx.x - GEMM_THREADS;  // 0..127
+      const int gt = threadIdx.x - 32 * FIRST_GATHER_WARP;  // 0..GATHER_THREADS-1
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -339,20 +347,22 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           // K-major A tile: 128 rows x 128 B.  8 consecutive threads fetch the 8 16-byte pieces of a row;
           // thread handles rows rb, rb+16, ...; the swizzle term (row & 7) is the same for all of them.
           static_assert(kLsuA && !A_MN, "ragged-M kernels gather a K-major A");
+          constexpr int RPP = GATHER_THREADS / 8;  // rows per pass: 16 or 32 (a multiple of 8)
+          constexpr int NPASS = BM / RPP;          // 8 or 4
           const int c = gt & 7, rb = gt >> 3;
           const uint32_t dst_off = rb * 128 + ((c ^ (rb & 7)) << 4);
-          const __nv_bfloat16* src[8];
+          const __nv_bfloat16* src[NPASS];
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const int r = tile.row0 + rb + 16 * i;
+          for (int i = 0; i < NPASS; ++i) {
+            const int r = tile.row0 + rb + RPP * i;
             const int idx = (r < p.total_rows) ? p.gather[r] : 0;
             src[i] = p.gather_src + static_cast<long long>(idx) * p.gather_ld + c * 8;
           }
           for (int kb = 0; kb < tile.num_kb; ++kb) {
-            if (!mbar_wait(smem_u32(&ss.empty[stage]), phase ^ 1u, abort_flag)) { ok = false; break; }
+            if (!mbar_wait_warp(smem_u32(&ss.empty[stage]), phase ^ 1u, abort_flag)) { ok = false; break; }
             const uint32_t dst = smem_u32(sA + stage * A_STAGE_BYTES) + dst_off;
 #pragma unroll
-            for (int i = 0; i < 8; ++i) cp_async16(dst + i * 2048, src[i] + kb * BK, 16);
+            for (int i = 0; i < NPASS; ++i) cp_async16(dst + i * (RPP * 128), src[i] + kb * BK, 16);
             cp_async_arrive_noinc(smem_u32(&ss.full[stage]));
             if (++stage == STAGES) { stage = 0; phase ^= 1u; }
           }
@@ -381,7 +391,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           };
           if (tile.num_kb > 0) load_idx(0);
           for (int kb = 0; kb < tile.num_kb; ++kb) {
-            if (!mbar_wait(smem_u32(&ss.empty[stage]), phase ^ 1u, abort_flag)) { ok = false; break; }
+            if (!mbar_wait_warp(smem_u32(&ss.empty[stage]), phase ^ 1u, abort_flag)) { ok = false; break; }
             const uint32_t dst = smem_u32(stage_base + stage * STAGE_BYTES) + chunk * CHUNK_BYTES;
 #pragma unroll
             for (int i = 0; i < PASSES; ++i) {
@@ -403,6 +413,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   // ---- epilogue -----------------------------------------------------------------------------
   else {
     const int quad = warp & 3;            // TMEM lanes [32*quad, 32*quad + 32) belong to this warp
+    constexpr int COL_SPLIT = EW / 4;     // warps sharing a lane quadrant split the accumulator's columns
+    constexpr int COLS_PER_WARP = BN / COL_SPLIT;
+    const int col_half = (warp - 2) >> 2; // 0 .. COL_SPLIT-1
     const int row_in_tile = quad * 32 + lane;
     int acc = 0;
     uint32_t acc_phase = 0;
@@ -413,7 +426,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       const bool row_ok = r < tile.row_end;
       const bool have_acc = tile.num_kb > 0;
       if (have_acc) {
-        if (!mbar_wait(smem_u32(&ss.acc_full[acc]), acc_phase, abort_flag)) { ok = false; break; }
+        if (!mbar_wait_warp(smem_u32(&ss.acc_full[acc]), acc_phase, abort_flag)) { ok = false; break; }
         tc_fence_after();
       }
       float score = 0.f;
@@ -427,7 +440,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       float ds_acc = 0.f;
       const uint32_t t_addr = tmem_base + acc * BN + (static_cast<uint32_t>(quad * 32) << 16);
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int c = col_half * (COLS_PER_WARP / 32); c < (col_half + 1) * (COLS_PER_WARP / 32); ++c) {
         const int n = tile.n0 + c * 32;
         if (n >= p.N) break;  // N is a multiple of 32: a chunk is entirely inside or entirely outside
         uint32_t v[32];
@@ -523,7 +536,16 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         }
       }
       if constexpr (EPI == EPI_DSWIGLU) {
-        if (row_ok) p.ds_partial[static_cast<long long>(tile.n0 / BN) * p.total_rows + r] = ds_acc;
+        // two partial rows per 256-column tile; with 4 epilogue warps one warp covers both halves
+        if (row_ok) {
+          float* dsp = p.ds_partial + static_cast<long long>(2 * (tile.n0 / BN)) * p.total_rows + r;
+          if constexpr (COL_SPLIT == 2) {
+            dsp[static_cast<long long>(col_half) * p.total_rows] = ds_acc;
+          } else {
+            dsp[0] = ds_acc;
+            dsp[p.total_rows] = 0.f;
+          }
+        }
       }
       if (have_acc) {
         tc_fence_before();
