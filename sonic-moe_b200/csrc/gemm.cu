@@ -1,5 +1,6 @@
 // Host side of the grouped GEMMs: tensor-map construction and the C-ABI launchers.
 #include "gemm.cuh"
+#include "gemm_pair.cuh"
 
 #include <cstdio>
 #include <cstdlib>
@@ -96,12 +97,72 @@ static int launch_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const 
   return cudaGetLastError() == cudaSuccess ? SMOE_OK : SMOE_ERR_LAUNCH;
 }
 
+// CTA-pair kernels (tcgen05.mma.cta_group::2, 256 x 256 tiles) are the default; SMOE_CTA_PAIR=0 selects
+// the single-CTA kernels (128 x 256 tiles).
+static bool use_cta_pair() {
+  static const bool v = env_int("SMOE_CTA_PAIR", 1) != 0;
+  return v;
+}
+
+template <bool RAGGED_K, bool A_GATHER, bool A_MN, bool B_GATHER, bool B_MN, int EPI, int EW, int GW>
+static int launch_pair_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p,
+                               cudaStream_t stream) {
+  auto kernel = pair::grouped_gemm_pair_kernel<RAGGED_K, A_GATHER, A_MN, B_GATHER, B_MN, EPI, EW, GW>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, pair::SMEM_BYTES) != cudaSuccess)
+      return SMOE_ERR_LAUNCH;
+    configured = true;
+  }
+  const int sms = num_sms();
+  if (sms < 2) return SMOE_ERR_DRIVER;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(sms & ~1), 1, 1);
+  cfg.blockDim = dim3(pair::threads(EW, GW), 1, 1);
+  cfg.dynamicSmemBytes = pair::SMEM_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, tmA, tmB, p) == cudaSuccess ? SMOE_OK : SMOE_ERR_LAUNCH;
+}
+
+// dflt_ew / dflt_gw: the tuned warp counts of the calling entry point.
+template <bool RAGGED_K, bool A_GATHER, bool A_MN, bool B_GATHER, bool B_MN, int EPI>
+static int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, cudaStream_t stream,
+                       int dflt_ew, int dflt_gw) {
+  static const int env_ew = env_int("SMOE_EPI_WARPS", 0);
+  static const int env_gw = env_int("SMOE_GATHER_WARPS", 0);
+  const int ew = (env_ew == 4 || env_ew == 8) ? env_ew : dflt_ew;
+  int gw = (env_gw == 4 || env_gw == 8) ? env_gw : dflt_gw;
+  constexpr bool kGather = A_GATHER || B_GATHER;
+#define SMOE_LAUNCH(EW_, GW_) \
+  return launch_pair_variant<RAGGED_K, A_GATHER, A_MN, B_GATHER, B_MN, EPI, EW_, GW_>(tmA, tmB, p, stream)
+  if constexpr (!kGather) {
+    if (ew == 4) SMOE_LAUNCH(4, 0);
+    SMOE_LAUNCH(8, 0);
+  } else {
+    if (gw != 8) gw = 4;
+    if (ew == 4 && gw == 4) SMOE_LAUNCH(4, 4);
+    if (ew == 4 && gw == 8) SMOE_LAUNCH(4, 8);
+    if (ew == 8 && gw == 4) SMOE_LAUNCH(8, 4);
+    SMOE_LAUNCH(8, 8);
+  }
+#undef SMOE_LAUNCH
+}
+
 // dflt_ew / dflt_gw: the tuned warp counts of the calling entry point.
 template <bool RAGGED_K, bool A_GATHER, bool A_MN, bool B_GATHER, bool B_MN, int EPI>
 static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, cudaStream_t stream,
                   int dflt_ew, int dflt_gw) {
   static const int env_ew = env_int("SMOE_EPI_WARPS", 0);
   static const int env_gw = env_int("SMOE_GATHER_WARPS", 0);
+  if (use_cta_pair())
+    return launch_pair<RAGGED_K, A_GATHER, A_MN, B_GATHER, B_MN, EPI>(tmA, tmB, p, stream, dflt_ew, dflt_gw);
   const int ew = (env_ew == 4 || env_ew == 8) ? env_ew : dflt_ew;
   int gw = (env_gw == 4 || env_gw == 8) ? env_gw : dflt_gw;
   constexpr bool kGather = A_GATHER || B_GATHER;
@@ -143,7 +204,7 @@ int smoe_up_projection_forward(const void* x, const void* w1, void* z, void* y1,
   if (TK == 0) return SMOE_OK;
   CUtensorMap tmA, tmB;
   SMOE_TRY(encode_2d(&tmA, x, T, H, H, 1, BK));                        // gather4 rows of x
-  SMOE_TRY(encode_2d(&tmB, w1, (uint64_t)E * 2 * I, H, H, BN, BK));    // W1[e] rows = output features, K-major
+  SMOE_TRY(encode_2d(&tmB, w1, (uint64_t)E * 2 * I, H, H, use_cta_pair() ? pair::BN_CTA : BN, BK));    // W1[e] rows = output features, K-major
   GemmParams p = {};
   p.E = E; p.N = 2 * I; p.K = H; p.total_rows = TK; p.gather_rows = T; p.b_rows_per_expert = 2 * I;
   p.off = expert_offset; p.gather = x_gather_idx;
@@ -160,7 +221,7 @@ int smoe_down_projection_forward(const void* y1, const void* w2, void* y2, const
   if (TK == 0) return SMOE_OK;
   CUtensorMap tmA, tmB;
   SMOE_TRY(encode_2d(&tmA, y1, TK, I, I, BM, BK));
-  SMOE_TRY(encode_2d(&tmB, w2, (uint64_t)E * H, I, I, BN, BK));        // W2[e] is (H, I): K-major
+  SMOE_TRY(encode_2d(&tmB, w2, (uint64_t)E * H, I, I, use_cta_pair() ? pair::BN_CTA : BN, BK));        // W2[e] is (H, I): K-major
   GemmParams p = {};
   p.E = E; p.N = H; p.K = I; p.total_rows = TK; p.b_rows_per_expert = H;
   p.off = expert_offset;
@@ -177,7 +238,7 @@ int smoe_down_projection_forward_scatter(const void* y1, const void* w2, float* 
   if (TK == 0) return SMOE_OK;
   CUtensorMap tmA, tmB;
   SMOE_TRY(encode_2d(&tmA, y1, TK, I, I, BM, BK));
-  SMOE_TRY(encode_2d(&tmB, w2, (uint64_t)E * H, I, I, BN, BK));
+  SMOE_TRY(encode_2d(&tmB, w2, (uint64_t)E * H, I, I, use_cta_pair() ? pair::BN_CTA : BN, BK));
   GemmParams p = {};
   p.E = E; p.N = H; p.K = I; p.total_rows = TK; p.gather_rows = T; p.b_rows_per_expert = H;
   p.off = expert_offset; p.gather = x_gather_idx; p.s_scatter = s_scatter_idx;

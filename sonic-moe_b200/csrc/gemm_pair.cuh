@@ -1,0 +1,438 @@
+// Grouped GEMM on CTA pairs: a cluster of two CTAs (one SM pair) computes a 256 x 256 output tile with
+// tcgen05.mma.cta_group::2.  Each CTA stages its own 128 rows of A and its own 128 of the tile's 256 B rows,
+// so a stage costs 32 KiB of shared-memory fill per CTA instead of 48 KiB and six stages fit; the
+// accumulator (this CTA's 128 rows x all 256 columns, fp32) lives in the CTA's own tensor memory, two
+// of them so the epilogue of one tile overlaps the main loop of the next.
+//
+// Roles per CTA (warp index):
+//   0        TMA producer for the operands that are not gathered (both CTAs; completion bytes are counted
+//            on the leader CTA's "full" barrier)
+//   1        leader CTA: MMA issuer.  other CTA: relay that forwards "my gathered rows have landed" to the
+//            leader's full barrier (kernels with a gathered operand), otherwise idle
+//   2..      EW epilogue warps (4 or 8)
+//   2+EW..   GW gather warps (0, 4 or 8): 16-byte cp.async row gathers into the swizzled stage
+//
+// Barriers.  full[s]: leader only; arrivals = 1 (leader's expect_tx) + 1 (relay, gathered kernels), tx =
+// TMA bytes of both CTAs.  gfull[s]: per CTA, one arrival per gather thread (cp.async completion).
+// empty[s], acc_full[a]: per CTA, signalled by the leader's multicast tcgen05.commit.  acc_empty[a]:
+// leader only, one arrival per epilogue warp of both CTAs.  Every wait is bounded (ptx.cuh).
+#pragma once
+#include "epilogue.cuh"
+#include "ptx.cuh"
+
+namespace smoe {
+namespace pair {
+
+constexpr int BM = 128;          // rows per CTA (TMEM lanes); the pair's tile has 2 * BM rows
+constexpr int BN = 256;          // tile columns = accumulator columns
+constexpr int BN_CTA = 128;      // B rows each CTA stages
+constexpr int BK = 64;
+constexpr int STAGES = 6;
+constexpr int UMMA_K = 16;
+constexpr int A_STAGE_BYTES = BM * BK * 2;       // 16 KiB
+constexpr int B_STAGE_BYTES = BN_CTA * BK * 2;   // 16 KiB
+constexpr int CHUNK_BYTES = BK * 128;            // 64-element MN chunk: BK rows x 128 B
+constexpr int MAX_EXPERTS = 1024;
+
+__host__ __device__ constexpr int threads(int epi_warps, int gather_warps) { return 32 * (2 + epi_warps + gather_warps); }
+
+struct SharedStorage {
+  uint64_t full[STAGES];
+  uint64_t gfull[STAGES];
+  uint64_t empty[STAGES];
+  uint64_t acc_full[2];
+  uint64_t acc_empty[2];
+  uint32_t tmem_base;
+  int abort_flag;
+  int m_tile_prefix[MAX_EXPERTS + 1];  // ragged-M: exclusive prefix of ceil(count / 256) per expert
+};
+
+constexpr int SMEM_BYTES = 1024 + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + sizeof(SharedStorage);
+
+struct Tile {
+  int e;
+  int row0;     // ragged-M: first grouped row of THIS CTA's 128 rows; ragged-K: first output row of this CTA
+  int row_end;  // ragged-M: off[e+1]; ragged-K: M
+  int n0;       // first column of the pair's 256-column tile
+  int k_begin, k_end;
+  int num_kb;
+};
+
+template <bool RAGGED_K>
+__device__ __forceinline__ bool decode_tile(const GemmParams& p, const SharedStorage& ss, long long t, int num_n,
+                                            uint32_t rank, Tile& tile) {
+  if constexpr (!RAGGED_K) {
+    const int total_m = ss.m_tile_prefix[p.E];
+    if (t >= static_cast<long long>(total_m) * num_n) return false;
+    const int mi = static_cast<int>(t / num_n);
+    const int ni = static_cast<int>(t % num_n);
+    int lo = 0, hi = p.E;
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (ss.m_tile_prefix[mid] <= mi) lo = mid; else hi = mid;
+    }
+    tile.e = lo;
+    tile.row0 = p.off[lo] + (mi - ss.m_tile_prefix[lo]) * (2 * BM) + static_cast<int>(rank) * BM;
+    tile.row_end = p.off[lo + 1];
+    tile.n0 = ni * BN;
+    tile.k_begin = 0;
+    tile.k_end = p.K;
+    tile.num_kb = p.K / BK;
+    return true;
+  } else {
+    const int num_m = (p.M + 2 * BM - 1) / (2 * BM);
+    const long long per_e = static_cast<long long>(num_m) * num_n;
+    if (t >= per_e * p.E) return false;
+    const int e = static_cast<int>(t / per_e);
+    const int rem = static_cast<int>(t % per_e);
+    tile.e = e;
+    tile.row0 = (rem / num_n) * (2 * BM) + static_cast<int>(rank) * BM;
+    tile.row_end = p.M;
+    tile.n0 = (rem % num_n) * BN;
+    tile.k_begin = p.off[e];
+    tile.k_end = p.off[e + 1];
+    tile.num_kb = (tile.k_end - tile.k_begin + BK - 1) / BK;
+    return true;
+  }
+}
+
+template <bool RAGGED_K, bool A_GATHER, bool A_MN, bool B_GATHER, bool B_MN, int EPI, int EW, int GW>
+__global__ void __launch_bounds__(threads(EW, GW), 1)
+grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                         const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + STAGES * A_STAGE_BYTES;
+  SharedStorage& ss = *reinterpret_cast<SharedStorage*>(smem + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES));
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();  // 0 = leader
+  const bool leader = rank == 0;
+  const long long first_tile = blockIdx.x >> 1;
+  const long long tile_step = gridDim.x >> 1;
+  volatile int* abort_flag = &ss.abort_flag;
+  const int num_n = (p.N + BN - 1) / BN;
+
+  constexpr bool kGather = A_GATHER || B_GATHER;
+  static_assert(!(A_GATHER && B_GATHER), "at most one operand is gathered");
+  static_assert(!kGather || GW > 0, "a gathered operand needs gather warps");
+  static_assert(EW == 4 || EW == 8, "4 or 8 epilogue warps");
+  constexpr int GATHER_THREADS = 32 * GW;
+  constexpr int FIRST_GATHER_WARP = 2 + EW;
+  constexpr uint32_t kTmaBytesPerCta = (A_GATHER ? 0 : A_STAGE_BYTES) + (B_GATHER ? 0 : B_STAGE_BYTES);
+
+  // ---- set-up -------------------------------------------------------------------------------
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(smem_u32(&ss.full[s]), 1 + (kGather ? 1 : 0));
+      mbar_init(smem_u32(&ss.gfull[s]), kGather ? GATHER_THREADS : 1);
+      mbar_init(smem_u32(&ss.empty[s]), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(smem_u32(&ss.acc_full[a]), 1);
+      mbar_init(smem_u32(&ss.acc_empty[a]), 2 * EW);
+    }
+    ss.abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&ss.tmem_base), 2 * BN);  // all 512 columns: both CTAs get the same base
+    tmem_relinquish();
+  }
+  if constexpr (!RAGGED_K) {
+    if (warp == 2) {
+      int running = 0;
+      for (int base = 0; base < p.E; base += 32) {
+        const int e = base + lane;
+        int v = 0;
+        if (e < p.E) v = (p.off[e + 1] - p.off[e] + 2 * BM - 1) / (2 * BM);
+        int incl = v;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+          const int o = __shfl_up_sync(0xffffffffu, incl, d);
+          if (lane >= d) incl += o;
+        }
+        if (e < p.E) ss.m_tile_prefix[e] = running + incl - v;
+        running += __shfl_sync(0xffffffffu, incl, 31);
+      }
+      if (lane == 0) ss.m_tile_prefix[p.E] = running;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // the other CTA's barriers are initialised before anything can arrive on them
+  tc_fence_after();
+  const uint32_t tmem_base = ss.tmem_base;
+
+  // ---- TMA producer -------------------------------------------------------------------------
+  if (warp == 0) {
+    if constexpr (kTmaBytesPerCta > 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      Tile tile;
+      for (long long t = first_tile; ok && decode_tile<RAGGED_K>(p, ss, t, num_n, rank, tile); t += tile_step) {
+        for (int kb = 0; kb < tile.num_kb; ++kb) {
+          if (!mbar_wait(smem_u32(&ss.empty[stage]), phase ^ 1u, abort_flag)) { ok = false; break; }
+          const uint32_t bar = map_to_cta(smem_u32(&ss.full[stage]), 0);  // the leader's barrier
+          const uint32_t a_dst = smem_u32(sA + stage * A_STAGE_BYTES);
+          const uint32_t b_dst = smem_u32(sB + stage * B_STAGE_BYTES);
+          if (leader && lane == 0) mbar_arrive_expect_tx(smem_u32(&ss.full[stage]), 2 * kTmaBytesPerCta);
+          __syncwarp();
+          const int k0 = RAGGED_K ? (tile.k_begin + kb * BK) : kb * BK;
+          if constexpr (!A_GATHER) {
+            if constexpr (!A_MN) {
+              if (lane == 0) tma_load_2d_pair(&tmA, bar, a_dst, k0, tile.row0);
+            } else {
+              if (lane < BM / 64) tma_load_2d_pair(&tmA, bar, a_dst + lane * CHUNK_BYTES, tile.row0 + 64 * lane, k0);
+            }
+          }
+          if constexpr (!B_GATHER) {
+            const int nb = tile.n0 + static_cast<int>(rank) * BN_CTA;  // this CTA's half of the B rows
+            if constexpr (!B_MN) {
+              if (lane == 0) tma_load_2d_pair(&tmB, bar, b_dst, k0, tile.e * p.b_rows_per_expert + nb);
+            } else {
+              const int krow = RAGGED_K ? k0 : (tile.e * p.b_rows_per_expert + k0);
+              if (lane < BN_CTA / 64) tma_load_2d_pair(&tmB, bar, b_dst + lane * CHUNK_BYTES, nb + 64 * lane, krow);
+            }
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+      if (!ok && lane == 0 && p.status) atomicCAS(p.status, ST_OK, ST_TIMEOUT_PRODUCER);
+    }
+  }
+  // ---- MMA issuer (leader) / gather relay (other CTA) ----------------------------------------
+  else if (warp == 1) {
+    if (leader) {
+      constexpr uint32_t idesc = make_idesc_bf16(2 * BM, BN, A_MN, B_MN);
+      constexpr uint32_t a_lbo = A_MN ? CHUNK_BYTES : 16;
+      constexpr uint32_t b_lbo = B_MN ? CHUNK_BYTES : 16;
+      constexpr uint32_t a_kstep = A_MN ? (UMMA_K * 128) : (UMMA_K * 2);
+      constexpr uint32_t b_kstep = B_MN ? (UMMA_K * 128) : (UMMA_K * 2);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      Tile tile;
+      for (long long t = first_tile; ok && decode_tile<RAGGED_K>(p, ss, t, num_n, rank, tile); t += tile_step) {
+        if (tile.num_kb == 0) continue;
+        if (!mbar_wait(smem_u32(&ss.acc_empty[acc]), acc_phase ^ 1u, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < tile.num_kb; ++kb) {
+          if (!mbar_wait(smem_u32(&ss.full[stage]), phase, abort_flag)) { ok = false; break; }
+          if constexpr (kGather) {
+            if (!mbar_wait(smem_u32(&ss.gfull[stage]), phase, abort_flag)) { ok = false; break; }
+          }
+          tc_fence_after();
+          if (lane == 0) {
+            if constexpr (kGather) fence_proxy_async_smem();
+            const uint64_t a_desc = make_smem_desc(smem_u32(sA + stage * A_STAGE_BYTES), a_lbo, 1024);
+            const uint64_t b_desc = make_smem_desc(smem_u32(sB + stage * B_STAGE_BYTES), b_lbo, 1024);
+#pragma unroll
+            for (int k4 = 0; k4 < BK / UMMA_K; ++k4) {
+              umma_bf16_pair(d_tmem, a_desc + ((k4 * a_kstep) >> 4), b_desc + ((k4 * b_kstep) >> 4), idesc,
+                             (kb > 0 || k4 > 0) ? 1u : 0u);
+            }
+            umma_commit_pair(smem_u32(&ss.empty[stage]), 3);  // frees the stage in both CTAs
+          }
+          __syncwarp();
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        if (lane == 0) umma_commit_pair(smem_u32(&ss.acc_full[acc]), 3);
+        __syncwarp();
+        if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+      }
+      if (!ok && lane == 0 && p.status) atomicCAS(p.status, ST_OK, ST_TIMEOUT_MMA);
+    } else {
+      if constexpr (kGather) {
+        // Relay: when this CTA's gather threads have filled a stage (their cp.async copies have landed and
+        // arrived on the local gfull barrier), count one arrival on the leader's full barrier.  The remote
+        // arrive is relaxed: a release at cluster scope costs about a microsecond per stage here, and the
+        // copies it would order have already completed when gfull flips.
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        Tile tile;
+        for (long long t = first_tile; ok && decode_tile<RAGGED_K>(p, ss, t, num_n, rank, tile); t += tile_step) {
+          for (int kb = 0; kb < tile.num_kb; ++kb) {
+            if (!mbar_wait(smem_u32(&ss.gfull[stage]), phase, abort_flag)) { ok = false; break; }
+            if (lane == 0) {
+              fence_proxy_async_smem();
+              mbar_arrive_cluster_relaxed(map_to_cta(smem_u32(&ss.full[stage]), 0));
+            }
+            __syncwarp();
+            if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+          }
+        }
+        if (!ok && lane == 0 && p.status) atomicCAS(p.status, ST_OK, ST_TIMEOUT_MMA);
+      }
+    }
+  }
+  // ---- gather producers ----------------------------------------------------------------------
+  else if (warp >= FIRST_GATHER_WARP) {
+    if constexpr (kGather) {
+      const int gt = threadIdx.x - 32 * FIRST_GATHER_WARP;
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      Tile tile;
+      for (long long t = first_tile; ok && decode_tile<RAGGED_K>(p, ss, t, num_n, rank, tile); t += tile_step) {
+        if constexpr (!RAGGED_K) {
+          // K-major A: 128 rows x 128 B; 8 consecutive threads fetch the 8 pieces of a row
+          static_assert(RAGGED_K || (A_GATHER && !A_MN), "ragged-M kernels gather a K-major A");
+          constexpr int RPP = GATHER_THREADS / 8;
+          constexpr int NPASS = BM / RPP;
+          const int c = gt & 7, rb = gt >> 3;
+          const uint32_t dst_off = rb * 128 + ((c ^ (rb & 7)) << 4);
+          const __nv_bfloat16* src[NPASS];
+#pragma unroll
+          for (int i = 0; i < NPASS; ++i) {
+            const int r = tile.row0 + rb + RPP * i;
+            const int idx = (r < p.total_rows) ? p.gather[r] : 0;
+            src[i] = p.gather_src + static_cast<long long>(idx) * p.gather_ld + c * 8;
+          }
+          for (int kb = 0; kb < tile.num_kb; ++kb) {
+            if (!mbar_wait(smem_u32(&ss.empty[stage]), phase ^ 1u, abort_flag)) { ok = false; break; }
+            const uint32_t dst = smem_u32(sA + stage * A_STAGE_BYTES) + dst_off;
+#pragma unroll
+#pragma unroll
+            for (int i = 0; i < NPASS; ++i) cp_async16(dst + i * (RPP * 128), src[i] + kb * BK, 16);
+            cp_async_arrive_noinc(smem_u32(&ss.gfull[stage]));
+            if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+          }
+        } else {
+          // MN-major: one token per 128-byte row; this CTA stages 128 elements of M (A) or N (B) = 2 chunks,
+          // i.e. 16 pieces of 16 B per token, fetched by 16 consecutive threads
+          constexpr int CPR = 16;
+          constexpr int ROWS_PER_PASS = GATHER_THREADS / CPR;
+          constexpr int PASSES = BK / ROWS_PER_PASS;
+          const int cc = gt % CPR, rb = gt / CPR;
+          const int chunk = cc >> 3, c = cc & 7;
+          const int col0 = (A_GATHER ? tile.row0 : tile.n0 + static_cast<int>(rank) * BN_CTA) + cc * 8;
+          const bool col_ok = col0 < (A_GATHER ? p.M : p.N);
+          const __nv_bfloat16* src_col = p.gather_src + col0;
+          uint8_t* stage_base = A_GATHER ? sA : sB;
+          constexpr int STAGE_BYTES = A_GATHER ? A_STAGE_BYTES : B_STAGE_BYTES;
+          // Source rows of three stages are kept in registers, loaded two stages before they are needed, so the
+          // latency of the index loads never sits between "stage is free" and "copies issued".
+          int idx0[PASSES], idx1[PASSES], idx2[PASSES];
+          auto load_idx = [&](int kb, int (&dst_idx)[PASSES]) {
+            const int k0 = tile.k_begin + kb * BK;
+#pragma unroll
+            for (int i = 0; i < PASSES; ++i) {
+              const int tok = k0 + rb + ROWS_PER_PASS * i;
+              dst_idx[i] = (kb < tile.num_kb && tok < tile.k_end && col_ok) ? p.gather[tok] : -1;
+            }
+          };
+          load_idx(0, idx0);
+          load_idx(1, idx1);
+          load_idx(2, idx2);
+          for (int kb = 0; kb < tile.num_kb; ++kb) {
+            if (!mbar_wait(smem_u32(&ss.empty[stage]), phase ^ 1u, abort_flag)) { ok = false; break; }
+            const uint32_t dst = smem_u32(stage_base + stage * STAGE_BYTES) + chunk * CHUNK_BYTES;
+#pragma unroll
+            for (int i = 0; i < PASSES; ++i) {
+              const int r = rb + ROWS_PER_PASS * i;
+              const bool valid = idx0[i] >= 0;
+              const __nv_bfloat16* src = src_col + static_cast<long long>(valid ? idx0[i] : 0) * p.gather_ld;
+              cp_async16(dst + r * 128 + ((c ^ (r & 7)) << 4), src, valid ? 16u : 0u);
+            }
+            cp_async_arrive_noinc(smem_u32(&ss.gfull[stage]));
+#pragma unroll
+            for (int i = 0; i < PASSES; ++i) { idx0[i] = idx1[i]; idx1[i] = idx2[i]; }
+            load_idx(kb + 3, idx2);
+            if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+          }
+        }
+      }
+      cp_async_wait_all();
+      if (!ok && (gt & 31) == 0 && p.status) atomicCAS(p.status, ST_OK, ST_TIMEOUT_PRODUCER);
+    }
+  }
+  // ---- epilogue -----------------------------------------------------------------------------
+  else {
+    const int quad = warp & 3;
+    constexpr int COL_SPLIT = EW / 4;
+    constexpr int COLS_PER_WARP = BN / COL_SPLIT;
+    const int col_half = (warp - 2) >> 2;
+    const int row_in_tile = quad * 32 + lane;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    Tile tile;
+    for (long long t = first_tile; ok && decode_tile<RAGGED_K>(p, ss, t, num_n, rank, tile); t += tile_step) {
+      const int r = tile.row0 + row_in_tile;
+      const bool row_ok = r < tile.row_end;
+      const bool have_acc = tile.num_kb > 0;
+      if (have_acc) {
+        if (!mbar_wait(smem_u32(&ss.acc_full[acc]), acc_phase, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+      }
+      float score = 0.f;
+      if constexpr (EPI == EPI_DSWIGLU || EPI == EPI_SCATTER) {
+        if (row_ok) score = load_score(p.scores, p.scores_are_bf16, p.s_scatter[r]);
+      }
+      float ds_acc = 0.f;
+      const uint32_t t_addr = tmem_base + acc * BN + (static_cast<uint32_t>(quad * 32) << 16);
+#pragma unroll 1
+      for (int c = col_half * (COLS_PER_WARP / 32); c < (col_half + 1) * (COLS_PER_WARP / 32); ++c) {
+        const int n = tile.n0 + c * 32;
+        if (n >= p.N) break;
+        uint32_t v[32];
+        if (have_acc) {
+          tmem_ld32(t_addr + c * 32, v);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = 0u;
+        }
+        if (!row_ok) continue;
+        epilogue_chunk<EPI, RAGGED_K>(p, tile.e, r, n, v, score, ds_acc);
+      }
+      if constexpr (EPI == EPI_DSWIGLU) {
+        if (row_ok) {
+          float* dsp = p.ds_partial + static_cast<long long>(2 * (tile.n0 / BN)) * p.total_rows + r;
+          if constexpr (COL_SPLIT == 2) {
+            dsp[static_cast<long long>(col_half) * p.total_rows] = ds_acc;
+          } else {
+            dsp[0] = ds_acc;
+            dsp[p.total_rows] = 0.f;
+          }
+        }
+      }
+      if (have_acc) {
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&ss.acc_empty[acc]), 0));
+        if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+      }
+    }
+    if (!ok && lane == 0 && p.status) atomicCAS(p.status, ST_OK, ST_TIMEOUT_EPILOGUE);
+  }
+
+  // ---- tear-down ----------------------------------------------------------------------------
+  if (*abort_flag != 0) {
+    const uint64_t t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // neither CTA leaves while the other may still signal its barriers or read its smem
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 2 * BN);
+  }
+}
+
+}  // namespace pair
+}  // namespace smoe
