@@ -141,7 +141,7 @@ int smoe_down_projection_forward_scatter(const void* y1, const void* w2, float* 
                                          void* stream);
 
 /* dy1 = dout[x_gather_idx[r]] @ W2[e]; y1 recomputed from z; dz = dswiglu(z) * dy1 * s, y1s = y1 * s,
- * ds_partial[c, r] = sum over the c-th 256-column block of dy1 * y1.  ds_partial has
+ * ds_partial[c, r] = sum over the c-th 128-column block of dy1 * y1.  ds_partial has
  * smoe_ds_partial_columns(I) * TK floats.  Replaces the dz kernel of sonicmoe::_down_projection_backward
  * (sonicmoe/functional/backward.py:286-389). */
 int smoe_down_projection_backward_act(const void* dout, const void* w2, const void* z, const void* scores,

@@ -33,8 +33,8 @@ def test_queries_and_argument_checks_without_gpu(built_library):
     from sonicmoe import _lib
 
     lib = _lib.lib
-    assert lib.smoe_ds_partial_columns(1024) == 4
-    assert lib.smoe_ds_partial_columns(64) == 1
+    assert lib.smoe_ds_partial_columns(1024) == 8   # one row of partials per 128 accumulator columns
+    assert lib.smoe_ds_partial_columns(64) == 2
     assert lib.smoe_route_metadata_workspace_bytes(128) >= 128 * 4
     # hidden size not a multiple of 64 -> shape error, nothing launched
     assert lib.smoe_up_projection_forward(None, None, None, None, None, None, 16, 100, 64, 8, 32, None, None) == -1
