@@ -138,7 +138,7 @@ static int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const Gem
   static const int env_ew = env_int("SMOE_EPI_WARPS", 0);
   static const int env_gw = env_int("SMOE_GATHER_WARPS", 0);
   const int ew = (env_ew == 4 || env_ew == 8) ? env_ew : dflt_ew;
-  int gw = (env_gw == 4 || env_gw == 8) ? env_gw : dflt_gw;
+  int gw = (env_gw == 4 || env_gw == 8 || env_gw == 16) ? env_gw : dflt_gw;
   constexpr bool kGather = A_GATHER || B_GATHER;
 #define SMOE_LAUNCH(EW_, GW_) \
   return launch_pair_variant<RAGGED_K, A_GATHER, A_MN, B_GATHER, B_MN, EPI, EW_, GW_>(tmA, tmB, p, stream)
@@ -146,6 +146,9 @@ static int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const Gem
     if (ew == 4) SMOE_LAUNCH(4, 0);
     SMOE_LAUNCH(8, 0);
   } else {
+    if constexpr (EPI != EPI_DSWIGLU) {  // 16 gather warps leave too few registers for the dSwiGLU epilogue
+      if (gw == 16) SMOE_LAUNCH(4, 16);
+    }
     if (gw != 8) gw = 4;
     if (ew == 4 && gw == 4) SMOE_LAUNCH(4, 4);
     if (ew == 4 && gw == 8) SMOE_LAUNCH(4, 8);

@@ -119,6 +119,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
   static_assert(!(A_GATHER && B_GATHER), "at most one operand is gathered");
   static_assert(!kGather || GW > 0, "a gathered operand needs gather warps");
   static_assert(EW == 4 || EW == 8, "4 or 8 epilogue warps");
+  static_assert(GW == 0 || GW == 4 || GW == 8 || GW == 16, "0, 4, 8 or 16 gather warps");
   constexpr int GATHER_THREADS = 32 * GW;
   constexpr int FIRST_GATHER_WARP = 2 + EW;
   constexpr uint32_t kTmaBytesPerCta = (A_GATHER ? 0 : A_STAGE_BYTES) + (B_GATHER ? 0 : B_STAGE_BYTES);
