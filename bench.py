@@ -403,6 +403,83 @@ def run_gpu_arm(args, rank, world, local_rank):
         dist.destroy_process_group()
 
 
+EP_CFG = dict(T=65536, H=2048, I=768, E=64, K=4)  # BASELINE configs[4]: tokens per GPU, Zipf-skewed routing
+
+
+def run_ep_arm(args, rank, world, local_rank):
+    """Expert-parallel, load-skewed layer (BASELINE configs[4]): T=65536 tokens per GPU, H=2048, I=768, E=64,
+    K=4, router logits biased by 2*log(1/rank_e) with a seeded permutation of expert ranks; experts sharded
+    over the ranks, dispatch/combine by NCCL all-to-all.  Not the default workload: `--workload ep_zipf`."""
+    import torch.distributed as dist
+
+    from sonicmoe import _lib
+    from sonicmoe.expert_parallel import moe_ep_softmax_topk_layer
+
+    cfg = EP_CFG
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", device_id=dev)
+    T, H, I, E, K = (cfg[k] for k in "THIEK")
+    e_local = E // world
+    g = torch.Generator(device=dev).manual_seed(0)
+    router_w = (torch.randn(E, H, generator=g, device=dev) * 0.02).bfloat16().requires_grad_(True)
+    ranks = torch.randperm(E, generator=g, device=dev) + 1
+    logit_bias = 2.0 * torch.log(1.0 / ranks.float())
+    g = torch.Generator(device=dev).manual_seed(1 + rank)
+    w1 = (torch.randn(e_local, 2 * I, H, generator=g, device=dev) * 0.02).bfloat16().requires_grad_(True)
+    w2 = (torch.randn(e_local, H, I, generator=g, device=dev) * 0.02).bfloat16().requires_grad_(True)
+    x = torch.randn(T, H, generator=g, device=dev).bfloat16().requires_grad_(True)
+    dout = torch.randn(T, H, generator=g, device=dev).bfloat16()
+    params = [x, router_w, w1, w2]
+    stats = {}
+
+    def step():
+        for p_ in params:
+            p_.grad = None
+        o, _logits, freq = moe_ep_softmax_topk_layer(x, router_w, w1, w2, K, E, logit_bias=logit_bias)
+        o.backward(dout)
+        stats["freq"] = freq
+
+    def barrier():
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    _lib.check_status(dev)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    freq = stats["freq"].float()
+    dist.all_reduce(freq)  # rows per expert over all ranks
+    _lib.check_status(dev)
+    if rank == 0:
+        ms_per_step = ms.item() / args.steps
+        total_rows = freq.sum().item()
+        value = 18.0 * total_rows * I * H / (ms_per_step * 1e-3) / 1e12
+        per_rank_rows = freq.view(world, e_local).sum(1)
+        line = {
+            "metric": "moe_fwd_bwd_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "tokens_per_s": world * T / (ms_per_step * 1e-3), "tflops_per_gpu": value / world,
+            "config": {"workload": "moe_layer_fwd_bwd_expert_parallel_zipf_T65536_per_gpu_H2048_I768_E64_K4", **cfg,
+                       "parallelism": f"ep{world}", "routing": "softmax_topk + per-expert logit bias 2*log(1/rank)"},
+            "expert_load_max_over_mean": (freq.max() / freq.mean()).item(),
+            "rank_load_max_over_mean": (per_rank_rows.max() / per_rank_rows.mean()).item(),
+        }
+        print(json.dumps(line), flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -414,6 +491,7 @@ def main():
     ap.add_argument("--tokens", type=int, default=CFG["T"])
     ap.add_argument("--experts", type=int, default=CFG["E"])
     ap.add_argument("--reps", type=int, default=5)
+    ap.add_argument("--workload", default="topk", choices=["topk", "ep_zipf"])
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -423,6 +501,13 @@ def main():
         return
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the layer has no CPU path (use --impl reference for the CPU arm)")
+    if args.workload == "ep_zipf":
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29541")
+        os.environ.setdefault("RANK", "0")
+        os.environ.setdefault("WORLD_SIZE", "1")
+        run_ep_arm(args, rank, world, local_rank)
+        return
     if args.kernels_only:
         cfg = dict(CFG, T=args.tokens, E=args.experts)
         dev = torch.device("cuda", local_rank)

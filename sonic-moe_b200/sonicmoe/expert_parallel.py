@@ -155,10 +155,11 @@ def received_row_experts(recv_counts: torch.Tensor) -> torch.Tensor:
 
 
 def moe_ep_softmax_topk_layer(x, router_w, w1_local, w2_local, K, num_experts, group=None, ops=None,
-                              is_inference_mode_enabled=False):
+                              is_inference_mode_enabled=False, logit_bias=None):
     """Expert-parallel token-choice top-K layer.
 
     x (T_local,H); router_w (E,H) replicated; w1_local (E/W,2I,H), w2_local (E/W,H,I): this rank's experts.
+    ``logit_bias`` (E,), optional, is added to the router logits before the top-k (load-skew experiments).
     Returns (o (T_local,H), router_logits (T_local,E), expert_frequency (E,) of this rank's tokens).
     """
     ops = ops or CudaOps()
@@ -172,6 +173,8 @@ def moe_ep_softmax_topk_layer(x, router_w, w1_local, w2_local, K, num_experts, g
     inference = is_inference_mode_enabled or not torch.is_grad_enabled()
 
     router_logits = F.linear(x if x.dtype == router_w.dtype else x.to(router_w.dtype), router_w)
+    if logit_bias is not None:
+        router_logits = router_logits + logit_bias.to(router_logits.dtype)
     scores, indices = ops.topk_softmax(router_logits, K)
     route = ops.route_metadata(indices.reshape(-1), num_experts, K)
 
