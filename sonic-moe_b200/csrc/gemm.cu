@@ -77,8 +77,12 @@ static int env_int(const char* name, int dflt) {
   const char* e = getenv(name);
   return (e != nullptr && e[0] != 0) ? atoi(e) : dflt;
 }
-static bool use_tma_gather() {
+static bool use_tma_gather() {  // single-CTA kernels: gather4 issued by the producer warp (slow, kept for comparison)
   static const bool v = env_int("SMOE_TMA_GATHER", 0) == 1;
+  return v;
+}
+static bool use_tma_gather_pair() {  // CTA-pair kernels: gather4 issued by 32 threads spread over the gather warps
+  static const bool v = env_int("SMOE_TMA_GATHER", 1) == 1;
   return v;
 }
 
@@ -104,10 +108,10 @@ static bool use_cta_pair() {
   return v;
 }
 
-template <bool RAGGED_K, bool A_GATHER, bool A_MN, bool B_GATHER, bool B_MN, int EPI, int EW, int GW>
+template <bool RAGGED_K, bool A_GATHER, bool A_MN, bool B_GATHER, bool B_MN, int EPI, int EW, int GW, bool TG = false>
 static int launch_pair_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p,
                                cudaStream_t stream) {
-  auto kernel = pair::grouped_gemm_pair_kernel<RAGGED_K, A_GATHER, A_MN, B_GATHER, B_MN, EPI, EW, GW>;
+  auto kernel = pair::grouped_gemm_pair_kernel<RAGGED_K, A_GATHER, A_MN, B_GATHER, B_MN, EPI, EW, GW, TG>;
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, pair::SMEM_BYTES) != cudaSuccess)
@@ -146,6 +150,10 @@ static int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const Gem
     if (ew == 4) SMOE_LAUNCH(4, 0);
     SMOE_LAUNCH(8, 0);
   } else {
+    if (use_tma_gather_pair()) {
+      if (gw == 8) return launch_pair_variant<RAGGED_K, A_GATHER, A_MN, B_GATHER, B_MN, EPI, 4, 8, true>(tmA, tmB, p, stream);
+      return launch_pair_variant<RAGGED_K, A_GATHER, A_MN, B_GATHER, B_MN, EPI, 4, 4, true>(tmA, tmB, p, stream);
+    }
     if constexpr (EPI != EPI_DSWIGLU) {  // 16 gather warps leave too few registers for the dSwiGLU epilogue
       if (gw == 16) SMOE_LAUNCH(4, 16);
     }
@@ -215,7 +223,7 @@ int smoe_up_projection_forward(const void* x, const void* w1, void* z, void* y1,
   p.out0 = static_cast<__nv_bfloat16*>(z); p.ld0 = 2 * I;
   p.out1 = static_cast<__nv_bfloat16*>(y1); p.ld1 = I;
   p.status = status;
-  return launch<false, true, false, false, false, EPI_SWIGLU>(tmA, tmB, p, static_cast<cudaStream_t>(stream), 4, 4);
+  return launch<false, true, false, false, false, EPI_SWIGLU>(tmA, tmB, p, static_cast<cudaStream_t>(stream), 4, 8);
 }
 
 int smoe_down_projection_forward(const void* y1, const void* w2, void* y2, const int* expert_offset, int H, int I,
@@ -268,7 +276,7 @@ int smoe_down_projection_backward_act(const void* dout, const void* w2, const vo
   p.z = static_cast<const __nv_bfloat16*>(z);
   p.scores = scores; p.scores_are_bf16 = scores_are_bf16; p.ds_partial = ds_partial;
   p.status = status;
-  return launch<false, true, false, false, true, EPI_DSWIGLU>(tmA, tmB, p, static_cast<cudaStream_t>(stream), 4, 4);
+  return launch<false, true, false, false, true, EPI_DSWIGLU>(tmA, tmB, p, static_cast<cudaStream_t>(stream), 4, 8);
 }
 
 int smoe_ds_partial_columns(int I) { return 2 * ((I + BN - 1) / BN); }

@@ -96,7 +96,9 @@ __device__ __forceinline__ bool decode_tile(const GemmParams& p, const SharedSto
   }
 }
 
-template <bool RAGGED_K, bool A_GATHER, bool A_MN, bool B_GATHER, bool B_MN, int EPI, int EW, int GW>
+// TG: the gather warps fetch rows with TMA tile::gather4 (32 issuing threads spread over the gather warps)
+// instead of 16-byte cp.async copies; completion then goes straight to the leader's full barrier.
+template <bool RAGGED_K, bool A_GATHER, bool A_MN, bool B_GATHER, bool B_MN, int EPI, int EW, int GW, bool TG = false>
 __global__ void __launch_bounds__(threads(EW, GW), 1)
 grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                          const GemmParams p) {
@@ -122,13 +124,15 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
   static_assert(GW == 0 || GW == 4 || GW == 8 || GW == 16, "0, 4, 8 or 16 gather warps");
   constexpr int GATHER_THREADS = 32 * GW;
   constexpr int FIRST_GATHER_WARP = 2 + EW;
-  constexpr uint32_t kTmaBytesPerCta = (A_GATHER ? 0 : A_STAGE_BYTES) + (B_GATHER ? 0 : B_STAGE_BYTES);
+  constexpr bool kLsuGather = kGather && !TG;  // gathered bytes arrive through cp.async (not counted as tx bytes)
+  constexpr uint32_t kTmaBytesPerCta =
+      (A_GATHER && !TG ? 0 : A_STAGE_BYTES) + (B_GATHER && !TG ? 0 : B_STAGE_BYTES);
 
   // ---- set-up -------------------------------------------------------------------------------
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(smem_u32(&ss.full[s]), 1 + (kGather ? 1 : 0));
-      mbar_init(smem_u32(&ss.gfull[s]), kGather ? GATHER_THREADS : 1);
+      mbar_init(smem_u32(&ss.full[s]), 1 + (kLsuGather ? 1 : 0));
+      mbar_init(smem_u32(&ss.gfull[s]), kLsuGather ? GATHER_THREADS : 1);
       mbar_init(smem_u32(&ss.empty[s]), 1);
     }
     for (int a = 0; a < 2; ++a) {
@@ -230,12 +234,12 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = 0; kb < tile.num_kb; ++kb) {
           if (!mbar_wait(smem_u32(&ss.full[stage]), phase, abort_flag)) { ok = false; break; }
-          if constexpr (kGather) {
+          if constexpr (kLsuGather) {
             if (!mbar_wait(smem_u32(&ss.gfull[stage]), phase, abort_flag)) { ok = false; break; }
           }
           tc_fence_after();
           if (lane == 0) {
-            if constexpr (kGather) fence_proxy_async_smem();
+            if constexpr (kLsuGather) fence_proxy_async_smem();
             const uint64_t a_desc = make_smem_desc(smem_u32(sA + stage * A_STAGE_BYTES), a_lbo, 1024);
             const uint64_t b_desc = make_smem_desc(smem_u32(sB + stage * B_STAGE_BYTES), b_lbo, 1024);
 #pragma unroll
@@ -255,7 +259,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       }
       if (!ok && lane == 0 && p.status) atomicCAS(p.status, ST_OK, ST_TIMEOUT_MMA);
     } else {
-      if constexpr (kGather) {
+      if constexpr (kLsuGather) {
         // Relay: when this CTA's gather threads have filled a stage (their cp.async copies have landed and
         // arrived on the local gfull barrier), count one arrival on the leader's full barrier.  The remote
         // arrive is relaxed: a release at cluster scope costs about a microsecond per stage here, and the
@@ -287,6 +291,58 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       uint32_t phase = 0;
       bool ok = true;
       Tile tile;
+      if constexpr (TG) {
+        // 32 issuing threads (every GATHER_THREADS/32-th thread, so they spread over all gather warps), each
+        // fetching 4 rows x 128 B per stage with one gather4.
+        constexpr int STRIDE = GATHER_THREADS / 32;
+        const bool issuer = (gt % STRIDE) == 0;
+        const int j = gt / STRIDE;  // 0..31
+        const CUtensorMap* tm = A_GATHER ? &tmA : &tmB;
+        uint8_t* stage_base = A_GATHER ? sA : sB;
+        constexpr int STAGE_BYTES = A_GATHER ? A_STAGE_BYTES : B_STAGE_BYTES;
+        for (long long t = first_tile; ok && decode_tile<RAGGED_K>(p, ss, t, num_n, rank, tile); t += tile_step) {
+          if constexpr (!RAGGED_K) {
+            int r4[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const int r = tile.row0 + 4 * j + i;
+              r4[i] = (r < p.total_rows) ? p.gather[r] : 0;
+            }
+            for (int kb = 0; kb < tile.num_kb; ++kb) {
+              if (!mbar_wait(smem_u32(&ss.empty[stage]), phase ^ 1u, abort_flag)) { ok = false; break; }
+              if (issuer)
+                tma_gather4_pair(tm, map_to_cta(smem_u32(&ss.full[stage]), 0),
+                                 smem_u32(stage_base + stage * STAGE_BYTES) + j * 512, kb * BK, r4[0], r4[1], r4[2],
+                                 r4[3]);
+              if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+            }
+          } else {
+            const int chunk = j >> 4, tq = j & 15;  // 2 chunks of 64 columns, 16 groups of 4 tokens
+            const int col0 = (A_GATHER ? tile.row0 : tile.n0 + static_cast<int>(rank) * BN_CTA) + 64 * chunk;
+            int cur[4], nxt[4];
+            auto load_idx = [&](int kb, int (&dst_idx)[4]) {
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const int tok = tile.k_begin + kb * BK + 4 * tq + i;
+                dst_idx[i] = (kb < tile.num_kb && tok < tile.k_end) ? p.gather[tok] : p.gather_rows;  // out of range: zeros
+              }
+            };
+            load_idx(0, cur);
+            load_idx(1, nxt);
+            for (int kb = 0; kb < tile.num_kb; ++kb) {
+              if (!mbar_wait(smem_u32(&ss.empty[stage]), phase ^ 1u, abort_flag)) { ok = false; break; }
+              if (issuer)
+                tma_gather4_pair(tm, map_to_cta(smem_u32(&ss.full[stage]), 0),
+                                 smem_u32(stage_base + stage * STAGE_BYTES) + chunk * CHUNK_BYTES + tq * 512, col0,
+                                 cur[0], cur[1], cur[2], cur[3]);
+#pragma unroll
+              for (int i = 0; i < 4; ++i) cur[i] = nxt[i];
+              load_idx(kb + 2, nxt);
+              if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+            }
+          }
+        }
+      } else
       for (long long t = first_tile; ok && decode_tile<RAGGED_K>(p, ss, t, num_n, rank, tile); t += tile_step) {
         if constexpr (!RAGGED_K) {
           // K-major A: 128 rows x 128 B; 8 consecutive threads fetch the 8 pieces of a row
@@ -305,7 +361,6 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
           for (int kb = 0; kb < tile.num_kb; ++kb) {
             if (!mbar_wait(smem_u32(&ss.empty[stage]), phase ^ 1u, abort_flag)) { ok = false; break; }
             const uint32_t dst = smem_u32(sA + stage * A_STAGE_BYTES) + dst_off;
-#pragma unroll
 #pragma unroll
             for (int i = 0; i < NPASS; ++i) cp_async16(dst + i * (RPP * 128), src[i] + kb * BK, 16);
             cp_async_arrive_noinc(smem_u32(&ss.gfull[stage]));

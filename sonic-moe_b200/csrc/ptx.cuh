@@ -105,6 +105,39 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
 }
 
+// Bounded wait for roles that are not on the critical path of the tensor pipe (epilogue and gather warps):
+// every probe lets the hardware park the thread until the phase flips or about a microsecond has passed,
+// so a dozen waiting warps do not keep hammering the barrier word in shared memory.
+__device__ __forceinline__ bool mbar_try_wait_parked(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(1000u)
+      : "memory");
+  return ok != 0;
+}
+
+__device__ __forceinline__ bool mbar_wait_parked(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try_wait_parked(bar, parity)) return true;
+  const uint64_t t0 = global_timer_ns();
+  uint32_t spins = 0;
+  while (true) {
+    if (mbar_try_wait_parked(bar, parity)) return true;
+    if ((++spins & 15u) == 0u) {
+      if (*abort_flag != 0) return false;
+      if (global_timer_ns() - t0 > kWaitLimitNs) {
+        *abort_flag = 1;
+        return false;
+      }
+    }
+  }
+}
+
 // Warp-wide wait: lane 0 watches the barrier, the other 31 lanes sleep at the warp barrier.  Must be
 // called by all 32 lanes.  The result is uniform across the warp.
 __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
@@ -253,6 +286,17 @@ __device__ __forceinline__ void tma_load_2d_pair(const CUtensorMap* d, uint32_t 
       "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, "
       "%4}], [%2];"
       ::"r"(dst), "l"(reinterpret_cast<uint64_t>(d)), "r"(bar_cluster_addr), "r"(x), "r"(y)
+      : "memory");
+}
+
+// Row gather (four rows of a 2D tensor, box {inner, 1}) into this CTA's shared memory, completion bytes counted
+// on a barrier given by its shared::cluster address.
+__device__ __forceinline__ void tma_gather4_pair(const CUtensorMap* d, uint32_t bar_cluster_addr, uint32_t dst, int x,
+                                                 int r0, int r1, int r2, int r3) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes [%0], "
+      "[%1, {%3, %4, %5, %6, %7}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(d)), "r"(bar_cluster_addr), "r"(x), "r"(r0), "r"(r1), "r"(r2), "r"(r3)
       : "memory");
 }
 
