@@ -167,6 +167,44 @@ int smoe_up_projection_weight_grad(const void* x, const void* dz, void* dw1, con
                                    const int* x_gather_idx, int T, int H, int I, int E, int TK, int* status,
                                    void* stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * FP8 (E4M3) path: fp32 block scales, scale = amax / 448 (1 for an all-zero block).  Activations: one scale
+ * per row and 128 consecutive columns; weights: one scale per 128 x 128 block of each expert's matrix.
+ * Requires H % 128 == 0 and I % 128 == 0.  The reference has no FP8 path: these entry points have the
+ * argument conventions of their bf16 counterparts above, with every fp8 operand followed by its scales.
+ * The weight-gradient GEMMs stay in bf16.
+ * ------------------------------------------------------------------------------------------- */
+
+/* q (rows, cols) uint8 E4M3 and scale (rows, cols/128) fp32 from x (rows, cols) bf16; cols % 128 == 0. */
+int smoe_fp8_quantize_rows(const void* x, void* q, float* scale, long long rows, int cols, void* stream);
+
+/* q (batch, rows, cols) and scale (batch, ceil(rows/128), cols/128) from w (batch, rows, cols) bf16. */
+int smoe_fp8_quantize_blocks(const void* w, void* q, float* scale, int batch, int rows, int cols, void* stream);
+
+/* As smoe_up_projection_forward with xq (T,H) + x_scale (T,H/128), w1q (E,2I,H) + w1_scale (E,2I/128,H/128);
+ * z, y1 are written in bf16. */
+int smoe_fp8_up_projection_forward(const void* xq, const float* x_scale, const void* w1q, const float* w1_scale,
+                                   void* z, void* y1, const int* expert_offset, const int* x_gather_idx, int T, int H,
+                                   int I, int E, int TK, int* status, void* stream);
+
+/* As smoe_down_projection_forward with y1q (TK,I) + y1_scale (TK,I/128), w2q (E,H,I) + w2_scale (E,H/128,I/128). */
+int smoe_fp8_down_projection_forward(const void* y1q, const float* y1_scale, const void* w2q, const float* w2_scale,
+                                     void* y2, const int* expert_offset, int H, int I, int E, int TK, int* status,
+                                     void* stream);
+
+/* As smoe_down_projection_backward_act with doutq (T,H) + dout_scale (T,H/128) and the quantised W2; z, dz, y1s bf16. */
+int smoe_fp8_down_projection_backward_act(const void* doutq, const float* dout_scale, const void* w2q,
+                                          const float* w2_scale, const void* z, const void* scores,
+                                          int scores_are_bf16, void* dz, void* y1s, float* ds_partial,
+                                          const int* expert_offset, const int* x_gather_idx,
+                                          const int* s_scatter_idx, int T, int H, int I, int E, int TK, int* status,
+                                          void* stream);
+
+/* As smoe_up_projection_backward_dx with dzq (TK,2I) + dz_scale (TK,2I/128) and the quantised W1. */
+int smoe_fp8_up_projection_backward_dx(const void* dzq, const float* dz_scale, const void* w1q, const float* w1_scale,
+                                       void* dx_expanded, const int* expert_offset, int H, int I, int E, int TK,
+                                       int* status, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,276 @@
+// FP8 (E4M3, fp32 block scales) entry points: quantisation kernels and the launchers of the FP8 grouped GEMMs.
+#include "gemm_fp8.cuh"
+
+#include <cuda_fp8.h>
+
+#include <cstdio>
+#include <cstdlib>
+#include <mutex>
+
+#include "../../include/sonicmoe_b200.h"
+
+namespace smoe {
+namespace fp8 {
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  });
+  return fn;
+}
+
+// 1-byte row-major 2D tensor (rows, cols); box (box_rows, box_cols <= 128), 128-byte swizzle.
+static int encode_u8(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows,
+                     uint32_t box_cols) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) return SMOE_ERR_DRIVER;
+  static thread_local bool context_bound = false;
+  if (!context_bound) {
+    if (cudaFree(nullptr) != cudaSuccess) return SMOE_ERR_DRIVER;
+    context_bound = true;
+  }
+  if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0 || cols % 16 != 0) return SMOE_ERR_ALIGNMENT;
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {cols};
+  const cuuint32_t box[2] = {box_cols, box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? SMOE_OK : SMOE_ERR_TENSORMAP;
+}
+
+static int num_sms() {
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) sms = 0;
+  }
+  return sms;
+}
+
+template <bool A_GATHER, bool B_MN, int EPI>
+static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, const Scales& sc,
+                  cudaStream_t stream) {
+  auto kernel = grouped_gemm_fp8_kernel<A_GATHER, B_MN, EPI>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
+      return SMOE_ERR_LAUNCH;
+    configured = true;
+  }
+  const int sms = num_sms();
+  if (sms < 2) return SMOE_ERR_DRIVER;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(sms & ~1), 1, 1);
+  cfg.blockDim = dim3(THREADS, 1, 1);
+  cfg.dynamicSmemBytes = SMEM_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, tmA, tmB, p, sc) == cudaSuccess ? SMOE_OK : SMOE_ERR_LAUNCH;
+}
+
+static bool bad_shape(int H, int I, int E) {
+  return H <= 0 || I <= 0 || E <= 0 || E > MAX_EXPERTS || (H % 128) != 0 || (I % 128) != 0;
+}
+
+// ---- quantisation ------------------------------------------------------------------------------------
+__device__ __forceinline__ uint8_t to_e4m3(float v) {
+  return static_cast<uint8_t>(__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3));
+}
+
+// One warp per (row, 128-column block): scale = amax / 448 (1 when the block is all zero), q = x / scale.
+__global__ void __launch_bounds__(256) quantize_rows_kernel(const __nv_bfloat16* __restrict__ x,
+                                                            uint8_t* __restrict__ q, float* __restrict__ scale,
+                                                            long long rows, int cols) {
+  const int blocks_per_row = cols >> 7;
+  const long long w = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (w >= rows * blocks_per_row) return;
+  const int lane = threadIdx.x & 31;
+  const long long row = w / blocks_per_row;
+  const int cb = static_cast<int>(w % blocks_per_row);
+  const uint2 raw = reinterpret_cast<const uint2*>(x + row * cols + cb * 128)[lane];
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+  const float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]);
+  float amax = fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(b.x), fabsf(b.y)));
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, d));
+  const float s = amax > 0.f ? amax / 448.f : 1.f;
+  const float inv = 1.f / s;
+  uint32_t packed = to_e4m3(a.x * inv) | (to_e4m3(a.y * inv) << 8) | (to_e4m3(b.x * inv) << 16) |
+                    (to_e4m3(b.y * inv) << 24);
+  reinterpret_cast<uint32_t*>(q + row * cols + cb * 128)[lane] = packed;
+  if (lane == 0) scale[row * blocks_per_row + cb] = s;
+}
+
+// One CTA per 128 x 128 block of a (batch, rows, cols) tensor; rows need not be a multiple of 128.
+__global__ void __launch_bounds__(256) quantize_blocks_kernel(const __nv_bfloat16* __restrict__ w,
+                                                              uint8_t* __restrict__ q, float* __restrict__ scale,
+                                                              int rows, int cols) {
+  __shared__ float warp_max[8];
+  const int cb = blockIdx.x, rb = blockIdx.y, e = blockIdx.z;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const long long base = (static_cast<long long>(e) * rows + static_cast<long long>(rb) * 128) * cols + cb * 128;
+  const int nrows = min(128, rows - rb * 128);
+  float amax = 0.f;
+  // pass 1: warp w scans rows 16w .. 16w+15 of the block (a lane covers 4 columns)
+  for (int rr = 0; rr < 16; ++rr) {
+    const int r = warp * 16 + rr;
+    if (r < nrows) {
+      const uint2 v = reinterpret_cast<const uint2*>(w + base + static_cast<long long>(r) * cols)[lane];
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+      const float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]);
+      amax = fmaxf(amax, fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(b.x), fabsf(b.y))));
+    }
+  }
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, d));
+  if (lane == 0) warp_max[warp] = amax;
+  __syncthreads();
+  amax = warp_max[0];
+#pragma unroll
+  for (int i = 1; i < 8; ++i) amax = fmaxf(amax, warp_max[i]);
+  const float s = amax > 0.f ? amax / 448.f : 1.f;
+  const float inv = 1.f / s;
+  // pass 2: the block is still in L1/L2
+  for (int rr = 0; rr < 16; ++rr) {
+    const int r = warp * 16 + rr;
+    if (r < nrows) {
+      const uint2 v = reinterpret_cast<const uint2*>(w + base + static_cast<long long>(r) * cols)[lane];
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+      const float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]);
+      const uint32_t packed = to_e4m3(a.x * inv) | (to_e4m3(a.y * inv) << 8) | (to_e4m3(b.x * inv) << 16) |
+                              (to_e4m3(b.y * inv) << 24);
+      reinterpret_cast<uint32_t*>(q + base + static_cast<long long>(r) * cols)[lane] = packed;
+    }
+  }
+  if (threadIdx.x == 0)
+    scale[(static_cast<long long>(e) * gridDim.y + rb) * gridDim.x + cb] = s;
+}
+
+}  // namespace fp8
+}  // namespace smoe
+
+using namespace smoe;
+using namespace smoe::fp8;
+
+#define SMOE_TRY(expr)              \
+  do {                              \
+    const int _rc = (expr);         \
+    if (_rc != SMOE_OK) return _rc; \
+  } while (0)
+
+extern "C" {
+
+int smoe_fp8_quantize_rows(const void* x, void* q, float* scale, long long rows, int cols, void* stream) {
+  if (rows < 0 || cols <= 0 || (cols % 128) != 0) return SMOE_ERR_SHAPE;
+  if (rows == 0) return SMOE_OK;
+  const long long warps = rows * (cols / 128);
+  quantize_rows_kernel<<<static_cast<unsigned>((warps + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), static_cast<uint8_t*>(q), scale, rows, cols);
+  return cudaGetLastError() == cudaSuccess ? SMOE_OK : SMOE_ERR_LAUNCH;
+}
+
+int smoe_fp8_quantize_blocks(const void* w, void* q, float* scale, int batch, int rows, int cols, void* stream) {
+  if (batch <= 0 || rows <= 0 || cols <= 0 || (cols % 128) != 0) return SMOE_ERR_SHAPE;
+  const dim3 grid(cols / 128, (rows + 127) / 128, batch);
+  quantize_blocks_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(w), static_cast<uint8_t*>(q), scale, rows, cols);
+  return cudaGetLastError() == cudaSuccess ? SMOE_OK : SMOE_ERR_LAUNCH;
+}
+
+int smoe_fp8_up_projection_forward(const void* xq, const float* x_scale, const void* w1q, const float* w1_scale,
+                                   void* z, void* y1, const int* expert_offset, const int* x_gather_idx, int T, int H,
+                                   int I, int E, int TK, int* status, void* stream) {
+  if (bad_shape(H, I, E) || T <= 0 || TK < 0) return SMOE_ERR_SHAPE;
+  if (TK == 0) return SMOE_OK;
+  CUtensorMap tmA, tmB;
+  SMOE_TRY(encode_u8(&tmA, xq, T, H, 1, BK));
+  SMOE_TRY(encode_u8(&tmB, w1q, (uint64_t)E * 2 * I, H, BN_CTA, BK));
+  GemmParams p = {};
+  p.E = E; p.N = 2 * I; p.K = H; p.total_rows = TK; p.gather_rows = T; p.b_rows_per_expert = 2 * I;
+  p.off = expert_offset; p.gather = x_gather_idx;
+  p.out0 = static_cast<__nv_bfloat16*>(z); p.ld0 = 2 * I;
+  p.out1 = static_cast<__nv_bfloat16*>(y1); p.ld1 = I;
+  p.status = status;
+  Scales sc = {x_scale, H / 128, w1_scale, (long long)(2 * I / 128) * (H / 128), H / 128, 1};
+  return launch<true, false, EPI_SWIGLU>(tmA, tmB, p, sc, static_cast<cudaStream_t>(stream));
+}
+
+int smoe_fp8_down_projection_forward(const void* y1q, const float* y1_scale, const void* w2q, const float* w2_scale,
+                                     void* y2, const int* expert_offset, int H, int I, int E, int TK, int* status,
+                                     void* stream) {
+  if (bad_shape(H, I, E) || TK < 0) return SMOE_ERR_SHAPE;
+  if (TK == 0) return SMOE_OK;
+  CUtensorMap tmA, tmB;
+  SMOE_TRY(encode_u8(&tmA, y1q, TK, I, BM, BK));
+  SMOE_TRY(encode_u8(&tmB, w2q, (uint64_t)E * H, I, BN_CTA, BK));
+  GemmParams p = {};
+  p.E = E; p.N = H; p.K = I; p.total_rows = TK; p.b_rows_per_expert = H;
+  p.off = expert_offset;
+  p.out0 = static_cast<__nv_bfloat16*>(y2); p.ld0 = H;
+  p.status = status;
+  Scales sc = {y1_scale, I / 128, w2_scale, (long long)(H / 128) * (I / 128), I / 128, 1};
+  return launch<false, false, EPI_STORE>(tmA, tmB, p, sc, static_cast<cudaStream_t>(stream));
+}
+
+int smoe_fp8_down_projection_backward_act(const void* doutq, const float* dout_scale, const void* w2q,
+                                          const float* w2_scale, const void* z, const void* scores,
+                                          int scores_are_bf16, void* dz, void* y1s, float* ds_partial,
+                                          const int* expert_offset, const int* x_gather_idx,
+                                          const int* s_scatter_idx, int T, int H, int I, int E, int TK, int* status,
+                                          void* stream) {
+  if (bad_shape(H, I, E) || TK < 0 || T <= 0) return SMOE_ERR_SHAPE;
+  if (TK == 0) return SMOE_OK;
+  CUtensorMap tmA, tmB;
+  SMOE_TRY(encode_u8(&tmA, doutq, T, H, 1, BK));
+  SMOE_TRY(encode_u8(&tmB, w2q, (uint64_t)E * H, I, BK, BN_CTA));  // W2[e] (H, I): rows are k
+  GemmParams p = {};
+  p.E = E; p.N = I; p.K = H; p.total_rows = TK; p.gather_rows = T; p.b_rows_per_expert = H;
+  p.off = expert_offset; p.gather = x_gather_idx; p.s_scatter = s_scatter_idx;
+  p.out0 = static_cast<__nv_bfloat16*>(dz); p.ld0 = 2 * I;
+  p.out1 = static_cast<__nv_bfloat16*>(y1s); p.ld1 = I;
+  p.z = static_cast<const __nv_bfloat16*>(z);
+  p.scores = scores; p.scores_are_bf16 = scores_are_bf16; p.ds_partial = ds_partial;
+  p.status = status;
+  // blocks of W2[e] are (h/128, i/128): k-block stride = I/128, n-block stride = 1
+  Scales sc = {dout_scale, H / 128, w2_scale, (long long)(H / 128) * (I / 128), 1, I / 128};
+  return launch<true, true, EPI_DSWIGLU>(tmA, tmB, p, sc, static_cast<cudaStream_t>(stream));
+}
+
+int smoe_fp8_up_projection_backward_dx(const void* dzq, const float* dz_scale, const void* w1q, const float* w1_scale,
+                                       void* dx_expanded, const int* expert_offset, int H, int I, int E, int TK,
+                                       int* status, void* stream) {
+  if (bad_shape(H, I, E) || TK < 0) return SMOE_ERR_SHAPE;
+  if (TK == 0) return SMOE_OK;
+  CUtensorMap tmA, tmB;
+  SMOE_TRY(encode_u8(&tmA, dzq, TK, 2 * I, BM, BK));
+  SMOE_TRY(encode_u8(&tmB, w1q, (uint64_t)E * 2 * I, H, BK, BN_CTA));  // W1[e] (2I, H): rows are k
+  GemmParams p = {};
+  p.E = E; p.N = H; p.K = 2 * I; p.total_rows = TK; p.b_rows_per_expert = 2 * I;
+  p.off = expert_offset;
+  p.out0 = static_cast<__nv_bfloat16*>(dx_expanded); p.ld0 = H;
+  p.status = status;
+  // blocks of W1[e] are (j/128, h/128): k-block stride = H/128, n-block stride = 1
+  Scales sc = {dz_scale, 2 * I / 128, w1_scale, (long long)(2 * I / 128) * (H / 128), 1, H / 128};
+  return launch<false, true, EPI_STORE>(tmA, tmB, p, sc, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

@@ -1,0 +1,155 @@
+"""FP8 (E4M3) expert path: activations quantised per row and 128 columns, weights per 128 x 128 block, fp32
+scales = amax / 448.  Forward and activation-gradient GEMMs run in FP8 on the tensor cores
+(`smoe_fp8_*` entry points); the weight-gradient GEMMs, the router and every saved tensor stay in bf16.
+
+The reference has no FP8 path; the functions mirror the bf16 ones of ``sonicmoe.functional``.
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.nn.functional as F
+
+from .. import _lib
+from .._lib import check, lib, ptr, stream_ptr
+from ..enums import ActivationType
+
+BLOCK = 128
+
+
+def quantize_rows(x: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """x (rows, cols) bf16 -> (q (rows, cols) uint8 holding E4M3, scale (rows, cols/128) fp32)."""
+    _lib.require_cuda(x, "x")
+    x = x.contiguous()
+    rows, cols = x.shape
+    dev = x.device
+    with torch.cuda.device(dev):
+        q = torch.empty(rows, cols, dtype=torch.uint8, device=dev)
+        s = torch.empty(rows, cols // BLOCK, dtype=torch.float32, device=dev)
+        check(lib.smoe_fp8_quantize_rows(x.data_ptr(), q.data_ptr(), s.data_ptr(), rows, cols, stream_ptr(dev)),
+              "fp8_quantize_rows")
+    return q, s
+
+
+def quantize_blocks(w: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """w (E, rows, cols) bf16 -> (q uint8, scale (E, ceil(rows/128), cols/128) fp32)."""
+    _lib.require_cuda(w, "w")
+    w = w.contiguous()
+    E, rows, cols = w.shape
+    dev = w.device
+    with torch.cuda.device(dev):
+        q = torch.empty(E, rows, cols, dtype=torch.uint8, device=dev)
+        s = torch.empty(E, (rows + BLOCK - 1) // BLOCK, cols // BLOCK, dtype=torch.float32, device=dev)
+        check(lib.smoe_fp8_quantize_blocks(w.data_ptr(), q.data_ptr(), s.data_ptr(), E, rows, cols, stream_ptr(dev)),
+              "fp8_quantize_blocks")
+    return q, s
+
+
+class _RoutedExpertsFp8(torch.autograd.Function):
+    """FP8 counterpart of ``_RoutedExperts``: same inputs, outputs and saved tensors (x, z, scores, indices)."""
+
+    @staticmethod
+    def forward(ctx, x, w1, w2, scores_flat, route, T: int, inference: bool):
+        from . import _expert_major
+
+        dev = x.device
+        x = x.contiguous()
+        w1e = _expert_major(w1)
+        w2e = _expert_major(w2)
+        E, two_i, H = w1e.shape
+        I = two_i // 2
+        TK = route.x_gather_idx.numel()
+        scores_flat = scores_flat.contiguous()
+        st = _lib.device_state(dev)
+        off = route.expert_frequency_offset.data_ptr()
+        xq, xs = quantize_rows(x)
+        w1q, w1s = quantize_blocks(w1e)
+        w2q, w2s = quantize_blocks(w2e)
+        with torch.cuda.device(dev):
+            stream = stream_ptr(dev)
+            z = torch.empty(TK, two_i, dtype=x.dtype, device=dev) if not inference else None
+            y1 = torch.empty(TK, I, dtype=x.dtype, device=dev)
+            check(lib.smoe_fp8_up_projection_forward(
+                xq.data_ptr(), xs.data_ptr(), w1q.data_ptr(), w1s.data_ptr(), ptr(z), y1.data_ptr(), off,
+                route.x_gather_idx.data_ptr(), T, H, I, E, TK, st.status.data_ptr(), stream), "fp8_up_projection_forward")
+            y1q, y1s = quantize_rows(y1)
+            y2 = torch.empty(TK, H, dtype=x.dtype, device=dev)
+            check(lib.smoe_fp8_down_projection_forward(
+                y1q.data_ptr(), y1s.data_ptr(), w2q.data_ptr(), w2s.data_ptr(), y2.data_ptr(), off, H, I, E, TK,
+                st.status.data_ptr(), stream), "fp8_down_projection_forward")
+            o = torch.empty(T, H, dtype=x.dtype, device=dev)
+            check(lib.smoe_gather_sum(
+                y2.data_ptr(), o.data_ptr(), scores_flat.data_ptr(), _lib.dtype_code(scores_flat.dtype),
+                route.s_reverse_scatter_idx.data_ptr(), ptr(route.token_offset), T, H, max(route.K, 1), stream),
+                "gather_sum")
+        if not inference:
+            ctx.save_for_backward(x, w1e, w2e, z, scores_flat)
+            ctx.route = route
+            ctx.dims = (T, H, I, E, TK)
+        return o
+
+    @staticmethod
+    def backward(ctx, dout):
+        x, w1e, w2e, z, scores_flat = ctx.saved_tensors
+        route = ctx.route
+        T, H, I, E, TK = ctx.dims
+        dev = x.device
+        dout = dout.contiguous().to(x.dtype)
+        st = _lib.device_state(dev)
+        off = route.expert_frequency_offset.data_ptr()
+        gat = route.x_gather_idx.data_ptr()
+        doutq, douts = quantize_rows(dout)
+        w1q, w1s = quantize_blocks(w1e)
+        w2q, w2s = quantize_blocks(w2e)
+        with torch.cuda.device(dev):
+            stream = stream_ptr(dev)
+            dz = torch.empty(TK, 2 * I, dtype=x.dtype, device=dev)
+            y1s = torch.empty(TK, I, dtype=x.dtype, device=dev)
+            ncols = lib.smoe_ds_partial_columns(I)
+            ds_partial = torch.empty(ncols, TK, dtype=torch.float32, device=dev)
+            check(lib.smoe_fp8_down_projection_backward_act(
+                doutq.data_ptr(), douts.data_ptr(), w2q.data_ptr(), w2s.data_ptr(), z.data_ptr(),
+                scores_flat.data_ptr(), int(scores_flat.dtype == torch.bfloat16), dz.data_ptr(), y1s.data_ptr(),
+                ds_partial.data_ptr(), off, gat, route.s_scatter_idx.data_ptr(), T, H, I, E, TK,
+                st.status.data_ptr(), stream), "fp8_down_projection_backward_act")
+            ds = torch.empty_like(scores_flat)
+            check(lib.smoe_ds_reduce(ds_partial.data_ptr(), route.s_scatter_idx.data_ptr(), ds.data_ptr(),
+                                     _lib.dtype_code(ds.dtype), TK, ncols, stream), "ds_reduce")
+            dw2 = torch.empty_like(w2e)
+            check(lib.smoe_down_projection_weight_grad(
+                dout.data_ptr(), y1s.data_ptr(), dw2.data_ptr(), off, gat, T, H, I, E, TK, st.status.data_ptr(),
+                stream), "down_projection_weight_grad")
+            dw1 = torch.empty_like(w1e)
+            check(lib.smoe_up_projection_weight_grad(
+                x.data_ptr(), dz.data_ptr(), dw1.data_ptr(), off, gat, T, H, I, E, TK, st.status.data_ptr(), stream),
+                "up_projection_weight_grad")
+            dzq, dzs = quantize_rows(dz)
+            dx_expanded = torch.empty(TK, H, dtype=x.dtype, device=dev)
+            check(lib.smoe_fp8_up_projection_backward_dx(
+                dzq.data_ptr(), dzs.data_ptr(), w1q.data_ptr(), w1s.data_ptr(), dx_expanded.data_ptr(), off, H, I, E,
+                TK, st.status.data_ptr(), stream), "fp8_up_projection_backward_dx")
+            dx = torch.empty(T, H, dtype=x.dtype, device=dev)
+            check(lib.smoe_gather_sum(
+                dx_expanded.data_ptr(), dx.data_ptr(), None, _lib.SMOE_F32, route.s_reverse_scatter_idx.data_ptr(),
+                ptr(route.token_offset), T, H, max(route.K, 1), stream), "gather_sum")
+        return dx, dw1.permute(1, 2, 0), dw2.permute(1, 2, 0), ds, None, None, None
+
+
+def moe_fp8_softmax_topk_layer(x, router_w, w1, b1, w2, b2, K, stream_id=0,
+                               activation_type: ActivationType | str = ActivationType.SWIGLU,
+                               is_inference_mode_enabled: bool = False):
+    """``moe_TC_softmax_topk_layer`` with the expert GEMMs of forward and activation gradients in FP8."""
+    from . import _check_experts_args, _route_metadata, topk_softmax
+
+    _check_experts_args(x, w1, w2, b1, b2, activation_type)
+    H = x.shape[1]
+    if H % BLOCK != 0 or (w1.shape[0] // 2) % BLOCK != 0:
+        raise ValueError("the FP8 path needs hidden and intermediate sizes that are multiples of 128")
+    E = router_w.size(0)
+    T = x.size(0)
+    router_logits = F.linear(x if x.dtype == router_w.dtype else x.to(router_w.dtype), router_w)
+    scores, indices = topk_softmax(router_logits, K)
+    route = _route_metadata(indices.reshape(-1), None, E, K)
+    inference = is_inference_mode_enabled or not torch.is_grad_enabled()
+    o = _RoutedExpertsFp8.apply(x, w1, w2, scores.reshape(-1), route, T, inference)
+    return o, router_logits, route.expert_frequency
