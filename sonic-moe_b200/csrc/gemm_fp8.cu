@@ -113,9 +113,8 @@ __global__ void __launch_bounds__(256) quantize_rows_kernel(const __nv_bfloat16*
 #pragma unroll
   for (int d = 16; d > 0; d >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, d));
   const float s = amax > 0.f ? amax / 448.f : 1.f;
-  const float inv = 1.f / s;
-  uint32_t packed = to_e4m3(a.x * inv) | (to_e4m3(a.y * inv) << 8) | (to_e4m3(b.x * inv) << 16) |
-                    (to_e4m3(b.y * inv) << 24);
+  // true division: a reciprocal of a denormal scale would overflow and turn the block's zeros into NaN
+  uint32_t packed = to_e4m3(a.x / s) | (to_e4m3(a.y / s) << 8) | (to_e4m3(b.x / s) << 16) | (to_e4m3(b.y / s) << 24);
   reinterpret_cast<uint32_t*>(q + row * cols + cb * 128)[lane] = packed;
   if (lane == 0) scale[row * blocks_per_row + cb] = s;
 }
@@ -148,7 +147,6 @@ __global__ void __launch_bounds__(256) quantize_blocks_kernel(const __nv_bfloat1
 #pragma unroll
   for (int i = 1; i < 8; ++i) amax = fmaxf(amax, warp_max[i]);
   const float s = amax > 0.f ? amax / 448.f : 1.f;
-  const float inv = 1.f / s;
   // pass 2: the block is still in L1/L2
   for (int rr = 0; rr < 16; ++rr) {
     const int r = warp * 16 + rr;
@@ -156,8 +154,8 @@ __global__ void __launch_bounds__(256) quantize_blocks_kernel(const __nv_bfloat1
       const uint2 v = reinterpret_cast<const uint2*>(w + base + static_cast<long long>(r) * cols)[lane];
       const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
       const float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]);
-      const uint32_t packed = to_e4m3(a.x * inv) | (to_e4m3(a.y * inv) << 8) | (to_e4m3(b.x * inv) << 16) |
-                              (to_e4m3(b.y * inv) << 24);
+      const uint32_t packed = to_e4m3(a.x / s) | (to_e4m3(a.y / s) << 8) | (to_e4m3(b.x / s) << 16) |
+                              (to_e4m3(b.y / s) << 24);
       reinterpret_cast<uint32_t*>(q + base + static_cast<long long>(r) * cols)[lane] = packed;
     }
   }

@@ -279,14 +279,24 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
         if (!mbar_wait(smem_u32(&ss.part_full[buf]), buf_phase, abort_flag)) { ok = false; break; }
         tc_fence_after();
         const uint32_t t_addr = tmem_base + buf * BN + col_half * 128 + (static_cast<uint32_t>(quad * 32) << 16);
+        // two register buffers: the load of the next 32 columns is in flight while this one is accumulated
+        uint32_t va[32], vb[32];
+        tmem_ld32(t_addr, va);
+        tmem_ld_wait();
+        tmem_ld32(t_addr + 32, vb);
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t v[32];
-          tmem_ld32(t_addr + c * 32, v);
-          tmem_ld_wait();
+        for (int i = 0; i < 32; ++i) acc[i] = fmaf(__uint_as_float(va[i]), scale, acc[i]);
+        tmem_ld_wait();
+        tmem_ld32(t_addr + 64, va);
 #pragma unroll
-          for (int i = 0; i < 32; ++i) acc[c * 32 + i] = fmaf(__uint_as_float(v[i]), scale, acc[c * 32 + i]);
-        }
+        for (int i = 0; i < 32; ++i) acc[32 + i] = fmaf(__uint_as_float(vb[i]), scale, acc[32 + i]);
+        tmem_ld_wait();
+        tmem_ld32(t_addr + 96, vb);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) acc[64 + i] = fmaf(__uint_as_float(va[i]), scale, acc[64 + i]);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) acc[96 + i] = fmaf(__uint_as_float(vb[i]), scale, acc[96 + i]);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive_cluster_relaxed(map_to_cta(smem_u32(&ss.part_empty[buf]), 0));
@@ -308,7 +318,8 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
         }
       }
       if constexpr (EPI == EPI_DSWIGLU) {
-        if (row_ok && cols_ok)
+        // every partial row the reduction reads is written, also the one past the last column block (zero)
+        if (row_ok)
           p.ds_partial[static_cast<long long>(2 * (tile.n0 / BN) + col_half) * p.total_rows + r] = ds_acc;
       }
     }
