@@ -353,9 +353,15 @@ def moe_TC_softmax_topk_layer(
     T = x.size(0)
     # a router kept in fp32 (an extension over the reference) computes its logits in fp32
     router_logits = F.linear(x if x.dtype == router_w.dtype else x.to(router_w.dtype), router_w)
+    inference = is_inference_mode_enabled or not torch.is_grad_enabled()
+    if torch.compiler.is_compiling():
+        # opaque custom ops instead of autograd functions with ctypes calls inside (torch.compile, fullgraph)
+        from .compiled_ops import layer_with_custom_ops
+
+        o, freq = layer_with_custom_ops(x, router_logits, w1, w2, K, E, inference)
+        return o, router_logits, freq
     scores, indices = topk_softmax(router_logits, K)
     route = _route_metadata(indices.reshape(-1), None, E, K)
-    inference = is_inference_mode_enabled or not torch.is_grad_enabled()
     o = _RoutedExperts.apply(x, w1, w2, scores.reshape(-1), route, T, inference)
     return o, router_logits, route.expert_frequency
 

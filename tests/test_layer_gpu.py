@@ -18,7 +18,7 @@ TOL = 1e-2
 
 def rel(a, b):
     a = a.detach().float().cpu()
-    b = torch.as_tensor(b).float()
+    b = torch.as_tensor(b).detach().float().cpu()
     return ((a - b).norm() / (b.norm() + 1e-30)).item()
 
 
@@ -208,3 +208,25 @@ def test_linearity_at_full_hidden_size(built_library):
     assert ((o12 - (0.5 * o1 + 2.0 * o2)).norm() / o12.norm()).item() < TOL
     torch.cuda.synchronize()
     _lib.check_status()
+
+
+def test_torch_compile_fullgraph_matches_eager(built_library):
+    """`torch.compile(fullgraph=True)` of the module (the reference compiles it in its tests and benchmarks,
+    tests/moe_test.py:80-81): same output and gradients as the eager module."""
+    from sonicmoe import _lib
+
+    T, H, I, E, K = 512, 256, 128, 16, 4
+    m, inp = _module(T, H, I, E, K, seed=9)
+    x = inp["x"].cuda().requires_grad_(True)
+    dout = inp["dout"].cuda()
+    o_ref, aux_ref = m(x)
+    g_ref = torch.autograd.grad(o_ref, [x, m.router.weight, m.c_fc.weight, m.c_proj.weight], dout)
+    compiled = torch.compile(m, fullgraph=True)
+    o, aux = compiled(x)
+    g = torch.autograd.grad(o, [x, m.router.weight, m.c_fc.weight, m.c_proj.weight], dout)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    assert torch.equal(o, o_ref)
+    assert rel(aux, aux_ref) < 1e-5
+    for a, b in zip(g, g_ref):
+        assert a.shape == b.shape and rel(a, b) < 1e-3
