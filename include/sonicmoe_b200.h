@@ -168,6 +168,41 @@ int smoe_up_projection_weight_grad(const void* x, const void* dz, void* dw1, con
                                    void* stream);
 
 /* ---------------------------------------------------------------------------------------------
+ * Any activation of the layer, and expert biases.  Activation codes: 0 swiglu, 1 geglu, 2 reglu (gated:
+ * W1[e] has 2I rows, gate row 2j / up row 2j+1), 3 relu_sq, 4 relu, 5 gelu (erf), 6 silu (W1[e] has I rows).
+ * N1 = rows of W1[e] (2I or I), a multiple of 128.  Biases are bf16 (E, N1) / (E, H) or NULL.
+ * ------------------------------------------------------------------------------------------- */
+
+/* z = x[gather] W1[e]^T + b1[e]; y1 = act(z).  z (TK,N1) or NULL; y1 (TK,I).  Replaces _up_projection_forward
+ * with a bias and any activation_type (sonicmoe/functional/forward.py:53-126, grouped_gemm.py:1170-1288, 2439-2452). */
+int smoe_up_projection_forward_act(const void* x, const void* w1, const void* b1, void* z, void* y1,
+                                   const int* expert_offset, const int* x_gather_idx, int T, int H, int N1, int E,
+                                   int TK, int activation, int* status, void* stream);
+
+/* y2 = y1 W2[e]^T + b2[e] (sonicmoe/functional/forward.py:132-175 with b2). */
+int smoe_down_projection_forward_bias(const void* y1, const void* w2, const void* b2, void* y2,
+                                      const int* expert_offset, int H, int I, int E, int TK, int* status,
+                                      void* stream);
+
+/* smoe_down_projection_backward_act for any activation: dz (TK,N1), y1s (TK,I), ds_partial as there. */
+int smoe_down_projection_backward_dact(const void* dout, const void* w2, const void* z, const void* scores,
+                                       int scores_are_bf16, void* dz, void* y1s, float* ds_partial,
+                                       const int* expert_offset, const int* x_gather_idx, const int* s_scatter_idx,
+                                       int T, int H, int I, int E, int TK, int activation, int* status,
+                                       void* stream);
+
+/* out[e, n] = sum over grouped rows r of expert e of w_r * src[row(r), n]; row(r) = gather_idx[r] (or r when NULL),
+ * w_r = scores[s_scatter_idx[r]] (or 1 when scores is NULL).  out bf16 (E,N).  db1 = column sums of dz, db2 = score-
+ * weighted column sums of dout rows.  Replaces db1_kernel / db2 of db2_and_ds_kernel (sonicmoe/functional/backward.py:36-168). */
+int smoe_expert_column_sum(const void* src, long long ld, const int* gather_idx, const void* scores,
+                           int scores_dtype, const int* s_scatter_idx, const int* expert_offset, void* out, int E,
+                           int N, void* stream);
+
+/* ds[s_scatter_idx[r]] += <dout[x_gather_idx[r], :], b2[e(r), :]> (the "ds += dout . b2" part of db2_and_ds_kernel). */
+int smoe_ds_add_bias_term(const void* dout, const void* b2, const int* expert_offset, const int* x_gather_idx,
+                          const int* s_scatter_idx, void* ds, int ds_dtype, int E, int H, int TK, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
  * FP8 (E4M3) path: fp32 block scales, scale = amax / 448 (1 for an all-zero block).  Activations: one scale
  * per row and 128 consecutive columns; weights: one scale per 128 x 128 block of each expert's matrix.
  * Requires H % 128 == 0 and I % 128 == 0.  The reference has no FP8 path: these entry points have the

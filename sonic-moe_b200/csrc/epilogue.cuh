@@ -10,7 +10,17 @@ enum Epilogue : int {
   EPI_SWIGLU = 1,   // out0[r, n] = bf16(acc) (unless out0 == nullptr); out1[r, n/2] = silu(acc[2j]) * acc[2j+1]
   EPI_DSWIGLU = 2,  // acc = dy1; reads z, score; writes dz (out0), y1*s (out1), per-row partial of ds
   EPI_SCATTER = 3,  // red.add fp32: acc_out[token(r), n] += score(r) * acc
+  // general forms: any activation of the layer, optional per-expert bias (GemmParams::act, ::bias)
+  EPI_ACT = 4,         // z = acc + b1 -> out0 (unless nullptr); y1 = act(z) (gated: act(z_even) * z_odd) -> out1
+  EPI_DACT = 5,        // acc = dy1; reads z, score; writes dz (out0), y1*s (out1), per-row partial of ds
+  EPI_STORE_BIAS = 6,  // out0[r, n] = bf16(acc + bias[e, n])
 };
+
+// Activation codes (GemmParams::act).  The first three are gated: the pre-activation has 2I columns,
+// gate = even column, up = odd column.
+enum Activation : int { ACT_SWIGLU = 0, ACT_GEGLU = 1, ACT_REGLU = 2, ACT_RELU_SQ = 3, ACT_RELU = 4, ACT_GELU = 5,
+                        ACT_SILU = 6 };
+__host__ __device__ constexpr bool act_is_gated(int act) { return act <= ACT_REGLU; }
 
 // Status codes written to GemmParams::status (first failure wins).
 enum Status : int { ST_OK = 0, ST_TIMEOUT_PRODUCER = 1, ST_TIMEOUT_MMA = 2, ST_TIMEOUT_EPILOGUE = 3 };
@@ -40,6 +50,9 @@ struct GemmParams {
   float* ds_partial;        // (2 * ceil(N/BN), total_rows) fp32: one row of partials per 128 accumulator columns
   float* acc_out;           // EPI_SCATTER: (gather_rows, N) fp32
   int* status;              // device word, 0 = ok
+  // general epilogues
+  const __nv_bfloat16* bias;  // (E, N) added to the accumulator, or nullptr
+  int act;                    // Activation code
 };
 
 __device__ __forceinline__ float load_score(const void* scores, int is_bf16, int slot) {
@@ -53,6 +66,70 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 }
 
 __device__ __forceinline__ float sigmoid_f(float x) { return __fdividef(1.0f, 1.0f + __expf(-x)); }
+
+// value and derivative of the elementwise function behind every activation of the layer
+__device__ __forceinline__ void act_value_grad(int act, float x, float& a, float& da) {
+  switch (act) {
+    case ACT_SWIGLU:
+    case ACT_SILU: {
+      const float sig = sigmoid_f(x);
+      a = x * sig;
+      da = sig * (1.f + x * (1.f - sig));
+      break;
+    }
+    case ACT_GEGLU:
+    case ACT_GELU: {  // exact (erf) GELU
+      const float cdf = 0.5f * (1.f + erff(x * 0.70710678118654752f));
+      a = x * cdf;
+      da = cdf + x * 0.3989422804014327f * __expf(-0.5f * x * x);
+      break;
+    }
+    case ACT_RELU_SQ: {
+      const float r = fmaxf(x, 0.f);
+      a = r * r;
+      da = 2.f * r;
+      break;
+    }
+    default: {  // ACT_REGLU, ACT_RELU
+      a = fmaxf(x, 0.f);
+      da = x > 0.f ? 1.f : 0.f;
+      break;
+    }
+  }
+}
+
+__device__ __forceinline__ void store_bf16x32(__nv_bfloat16* dst, const float (&f)[32]) {
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    uint4 w;
+    w.x = pack_bf16(f[8 * j + 0], f[8 * j + 1]);
+    w.y = pack_bf16(f[8 * j + 2], f[8 * j + 3]);
+    w.z = pack_bf16(f[8 * j + 4], f[8 * j + 5]);
+    w.w = pack_bf16(f[8 * j + 6], f[8 * j + 7]);
+    reinterpret_cast<uint4*>(dst)[j] = w;
+  }
+}
+
+// acc (+ bias) as 32 floats
+__device__ __forceinline__ void load_biased(const GemmParams& p, int expert, int n, const uint32_t (&v)[32],
+                                            float (&f)[32]) {
+#pragma unroll
+  for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+  if (p.bias != nullptr) {
+    const uint4* b = reinterpret_cast<const uint4*>(p.bias + static_cast<long long>(expert) * p.N + n);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const uint4 w = b[j];
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&w);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 t = __bfloat1622float2(h[i]);
+        f[8 * j + 2 * i] += t.x;
+        f[8 * j + 2 * i + 1] += t.y;
+      }
+    }
+  }
+}
 
 // One 32-column piece of one accumulator row: v[j] = acc[r, n + j] (fp32 bits).  `r` is the grouped row
 // (ragged-M) or the output row inside the expert's matrix (ragged-K); only called for rows that exist.
@@ -130,6 +207,86 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, int expert, 
       reinterpret_cast<uint4*>(dz_dst)[2 * j + 1] = make_uint4(dzw[4], dzw[5], dzw[6], dzw[7]);
       reinterpret_cast<uint4*>(ys_dst)[j] = make_uint4(pack_bf16(ys[0], ys[1]), pack_bf16(ys[2], ys[3]),
                                                        pack_bf16(ys[4], ys[5]), pack_bf16(ys[6], ys[7]));
+    }
+  } else if constexpr (EPI == EPI_STORE_BIAS) {
+    float f[32];
+    load_biased(p, expert, n, v, f);
+    store_bf16x32(p.out0 + r * p.ld0 + n, f);
+  } else if constexpr (EPI == EPI_ACT) {
+    float f[32];
+    load_biased(p, expert, n, v, f);
+    if (p.out0 != nullptr) store_bf16x32(p.out0 + r * p.ld0 + n, f);
+    if (act_is_gated(p.act)) {
+      float y[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        float a, da;
+        act_value_grad(p.act, f[2 * j], a, da);
+        y[j] = a * f[2 * j + 1];
+      }
+      __nv_bfloat16* dst1 = p.out1 + r * p.ld1 + (n >> 1);
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+        reinterpret_cast<uint4*>(dst1)[j] = make_uint4(pack_bf16(y[8 * j], y[8 * j + 1]), pack_bf16(y[8 * j + 2], y[8 * j + 3]),
+                                                       pack_bf16(y[8 * j + 4], y[8 * j + 5]), pack_bf16(y[8 * j + 6], y[8 * j + 7]));
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        float a, da;
+        act_value_grad(p.act, f[j], a, da);
+        f[j] = a;
+      }
+      store_bf16x32(p.out1 + r * p.ld1 + n, f);
+    }
+  } else if constexpr (EPI == EPI_DACT) {
+    // acc[., i] = dy1[r, i]
+    if (act_is_gated(p.act)) {
+      const uint4* zsrc = reinterpret_cast<const uint4*>(p.z + static_cast<long long>(r) * (2ll * p.N) + 2 * n);
+      __nv_bfloat16* dz_dst = p.out0 + r * p.ld0 + 2 * n;
+      __nv_bfloat16* ys_dst = p.out1 + r * p.ld1 + n;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const uint4 za = zsrc[2 * j], zb = zsrc[2 * j + 1];
+        const uint32_t zw[8] = {za.x, za.y, za.z, za.w, zb.x, zb.y, zb.z, zb.w};
+        uint32_t dzw[8];
+        float ys[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const __nv_bfloat162 gu = *reinterpret_cast<const __nv_bfloat162*>(&zw[i]);
+          const float g = __low2float(gu), u = __high2float(gu);
+          const float dy = __uint_as_float(v[8 * j + i]);
+          float a, da;
+          act_value_grad(p.act, g, a, da);
+          const float y1 = a * u;
+          ds_acc += dy * y1;
+          dzw[i] = pack_bf16(dy * u * da * score, dy * a * score);
+          ys[i] = y1 * score;
+        }
+        reinterpret_cast<uint4*>(dz_dst)[2 * j] = make_uint4(dzw[0], dzw[1], dzw[2], dzw[3]);
+        reinterpret_cast<uint4*>(dz_dst)[2 * j + 1] = make_uint4(dzw[4], dzw[5], dzw[6], dzw[7]);
+        reinterpret_cast<uint4*>(ys_dst)[j] = make_uint4(pack_bf16(ys[0], ys[1]), pack_bf16(ys[2], ys[3]),
+                                                         pack_bf16(ys[4], ys[5]), pack_bf16(ys[6], ys[7]));
+      }
+    } else {
+      const uint4* zsrc = reinterpret_cast<const uint4*>(p.z + static_cast<long long>(r) * p.N + n);
+      float dzf[32], ysf[32];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const uint4 zq = zsrc[j];
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&zq);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float zval = (i & 1) ? __high2float(h[i >> 1]) : __low2float(h[i >> 1]);
+          const float dy = __uint_as_float(v[8 * j + i]);
+          float a, da;
+          act_value_grad(p.act, zval, a, da);
+          ds_acc += dy * a;
+          dzf[8 * j + i] = dy * da * score;
+          ysf[8 * j + i] = a * score;
+        }
+      }
+      store_bf16x32(p.out0 + r * p.ld0 + n, dzf);
+      store_bf16x32(p.out1 + r * p.ld1 + n, ysf);
     }
   } else if constexpr (EPI == EPI_SCATTER) {
     float* dst = p.acc_out + static_cast<long long>(p.gather[r]) * p.N + n;

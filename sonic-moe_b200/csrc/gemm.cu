@@ -279,6 +279,72 @@ int smoe_down_projection_backward_act(const void* dout, const void* w2, const vo
   return launch<false, true, false, false, true, EPI_DSWIGLU>(tmA, tmB, p, static_cast<cudaStream_t>(stream), 4, 8);
 }
 
+// ---- general activations and biases (CTA-pair kernels only) ---------------------------------------------
+static bool bad_activation(int a) { return a < ACT_SWIGLU || a > ACT_SILU; }
+
+int smoe_up_projection_forward_act(const void* x, const void* w1, const void* b1, void* z, void* y1,
+                                   const int* expert_offset, const int* x_gather_idx, int T, int H, int N1, int E,
+                                   int TK, int activation, int* status, void* stream) {
+  if (bad_activation(activation) || H <= 0 || (H % 64) != 0 || N1 <= 0 || (N1 % 128) != 0 || E <= 0 ||
+      E > MAX_EXPERTS || T <= 0 || TK < 0)
+    return SMOE_ERR_SHAPE;
+  if (TK == 0) return SMOE_OK;
+  CUtensorMap tmA, tmB;
+  SMOE_TRY(encode_2d(&tmA, x, T, H, H, 1, BK));
+  SMOE_TRY(encode_2d(&tmB, w1, (uint64_t)E * N1, H, H, pair::BN_CTA, BK));
+  GemmParams p = {};
+  p.E = E; p.N = N1; p.K = H; p.total_rows = TK; p.gather_rows = T; p.b_rows_per_expert = N1;
+  p.off = expert_offset; p.gather = x_gather_idx;
+  p.gather_src = static_cast<const __nv_bfloat16*>(x); p.gather_ld = H;
+  p.out0 = static_cast<__nv_bfloat16*>(z); p.ld0 = N1;
+  p.out1 = static_cast<__nv_bfloat16*>(y1); p.ld1 = act_is_gated(activation) ? N1 / 2 : N1;
+  p.bias = static_cast<const __nv_bfloat16*>(b1); p.act = activation;
+  p.status = status;
+  return launch_pair<false, true, false, false, false, EPI_ACT>(tmA, tmB, p, static_cast<cudaStream_t>(stream), 4, 8);
+}
+
+int smoe_down_projection_forward_bias(const void* y1, const void* w2, const void* b2, void* y2,
+                                      const int* expert_offset, int H, int I, int E, int TK, int* status,
+                                      void* stream) {
+  if (bad_shape(H, I, E) || TK < 0) return SMOE_ERR_SHAPE;
+  if (TK == 0) return SMOE_OK;
+  CUtensorMap tmA, tmB;
+  SMOE_TRY(encode_2d(&tmA, y1, TK, I, I, BM, BK));
+  SMOE_TRY(encode_2d(&tmB, w2, (uint64_t)E * H, I, I, pair::BN_CTA, BK));
+  GemmParams p = {};
+  p.E = E; p.N = H; p.K = I; p.total_rows = TK; p.b_rows_per_expert = H;
+  p.off = expert_offset;
+  p.out0 = static_cast<__nv_bfloat16*>(y2); p.ld0 = H;
+  p.bias = static_cast<const __nv_bfloat16*>(b2);
+  p.status = status;
+  return launch_pair<false, false, false, false, false, EPI_STORE_BIAS>(tmA, tmB, p,
+                                                                        static_cast<cudaStream_t>(stream), 4, 0);
+}
+
+int smoe_down_projection_backward_dact(const void* dout, const void* w2, const void* z, const void* scores,
+                                       int scores_are_bf16, void* dz, void* y1s, float* ds_partial,
+                                       const int* expert_offset, const int* x_gather_idx, const int* s_scatter_idx,
+                                       int T, int H, int I, int E, int TK, int activation, int* status,
+                                       void* stream) {
+  if (bad_activation(activation) || bad_shape(H, I, E) || TK < 0 || T <= 0) return SMOE_ERR_SHAPE;
+  if (TK == 0) return SMOE_OK;
+  CUtensorMap tmA, tmB;
+  SMOE_TRY(encode_2d(&tmA, dout, T, H, H, 1, BK));
+  SMOE_TRY(encode_2d(&tmB, w2, (uint64_t)E * H, I, I, BK, 64));
+  const int n1 = act_is_gated(activation) ? 2 * I : I;
+  GemmParams p = {};
+  p.E = E; p.N = I; p.K = H; p.total_rows = TK; p.gather_rows = T; p.b_rows_per_expert = H;
+  p.off = expert_offset; p.gather = x_gather_idx; p.s_scatter = s_scatter_idx;
+  p.gather_src = static_cast<const __nv_bfloat16*>(dout); p.gather_ld = H;
+  p.out0 = static_cast<__nv_bfloat16*>(dz); p.ld0 = n1;
+  p.out1 = static_cast<__nv_bfloat16*>(y1s); p.ld1 = I;
+  p.z = static_cast<const __nv_bfloat16*>(z);
+  p.scores = scores; p.scores_are_bf16 = scores_are_bf16; p.ds_partial = ds_partial;
+  p.act = activation;
+  p.status = status;
+  return launch_pair<false, true, false, false, true, EPI_DACT>(tmA, tmB, p, static_cast<cudaStream_t>(stream), 4, 8);
+}
+
 int smoe_ds_partial_columns(int I) { return 2 * ((I + BN - 1) / BN); }
 
 int smoe_up_projection_backward_dx(const void* dz, const void* w1, void* dx_expanded, const int* expert_offset, int H,

@@ -435,7 +435,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         tc_fence_after();
       }
       float score = 0.f;
-      if constexpr (EPI == EPI_DSWIGLU || EPI == EPI_SCATTER) {
+      if constexpr (EPI == EPI_DSWIGLU || EPI == EPI_DACT || EPI == EPI_SCATTER) {
         if (row_ok) score = load_score(p.scores, p.scores_are_bf16, p.s_scatter[r]);
       }
       float ds_acc = 0.f;
@@ -455,7 +455,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         if (!row_ok) continue;
         epilogue_chunk<EPI, RAGGED_K>(p, tile.e, r, n, v, score, ds_acc);
       }
-      if constexpr (EPI == EPI_DSWIGLU) {
+      if constexpr (EPI == EPI_DSWIGLU || EPI == EPI_DACT) {
         if (row_ok) {
           float* dsp = p.ds_partial + static_cast<long long>(2 * (tile.n0 / BN)) * p.total_rows + r;
           if constexpr (COL_SPLIT == 2) {

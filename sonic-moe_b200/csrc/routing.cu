@@ -427,6 +427,84 @@ static int noalloc_scratch(int** out) {
   return SMOE_OK;
 }
 
+// out[e, n] = sum over the grouped rows r of expert e of w_r * src[row(r), n]   (bias gradients)
+//   row(r) = gather[r] or r;  w_r = scores[s_scatter[r]] or 1.  One CTA per (expert, 256 columns):
+//   warp w takes rows w, w+8, ...; a lane covers 8 columns; partial sums meet in shared memory.
+template <typename ScoreT>
+__global__ void __launch_bounds__(256) expert_column_sum_kernel(const __nv_bfloat16* __restrict__ src, long long ld,
+                                                                const int* __restrict__ gather,
+                                                                const ScoreT* __restrict__ scores,
+                                                                const int* __restrict__ s_scatter,
+                                                                const int* __restrict__ off,
+                                                                __nv_bfloat16* __restrict__ out, int N) {
+  __shared__ float part[8][256];
+  const int e = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int col = blockIdx.y * 256 + lane * 8;
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  if (col < N) {
+    for (int r = off[e] + warp; r < off[e + 1]; r += 8) {
+      const long long row = gather != nullptr ? gather[r] : r;
+      const float w = scores != nullptr ? static_cast<float>(scores[s_scatter[r]]) : 1.f;
+      const uint4 v = *reinterpret_cast<const uint4*>(src + row * ld + col);
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(h[j]);
+        acc[2 * j] += w * f.x;
+        acc[2 * j + 1] += w * f.y;
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) part[warp][lane * 8 + j] = acc[j];
+  __syncthreads();
+  const int c = threadIdx.x;
+  if (blockIdx.y * 256 + c < N) {
+    float s = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) s += part[w][c];
+    out[static_cast<long long>(e) * N + blockIdx.y * 256 + c] = __float2bfloat16(s);
+  }
+}
+
+// ds[s_scatter[r]] += <dout[gather[r], :], b2[e(r), :]>: the part of the score gradient that comes from the
+// down-projection bias.  One warp per grouped row; the expert of a row by binary search in the offsets.
+template <typename DsT>
+__global__ void __launch_bounds__(256) ds_bias_term_kernel(const __nv_bfloat16* __restrict__ dout,
+                                                           const __nv_bfloat16* __restrict__ b2,
+                                                           const int* __restrict__ off, const int* __restrict__ gather,
+                                                           const int* __restrict__ s_scatter, DsT* __restrict__ ds,
+                                                           int E, int H, int TK) {
+  const int lane = threadIdx.x & 31;
+  const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (r >= TK) return;
+  int lo = 0, hi = E;
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (off[mid] <= r) lo = mid; else hi = mid;
+  }
+  const __nv_bfloat16* a = dout + static_cast<long long>(gather[r]) * H;
+  const __nv_bfloat16* b = b2 + static_cast<long long>(lo) * H;
+  float acc = 0.f;
+  for (int c = lane * 8; c < H; c += 256) {
+    const uint4 va = *reinterpret_cast<const uint4*>(a + c), vb = *reinterpret_cast<const uint4*>(b + c);
+    const __nv_bfloat162* ha = reinterpret_cast<const __nv_bfloat162*>(&va);
+    const __nv_bfloat162* hb = reinterpret_cast<const __nv_bfloat162*>(&vb);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 fa = __bfloat1622float2(ha[j]), fb = __bfloat1622float2(hb[j]);
+      acc += fa.x * fb.x + fa.y * fb.y;
+    }
+  }
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, d);
+  if (lane == 0) {
+    const int slot = s_scatter[r];
+    ds[slot] = static_cast<DsT>(static_cast<float>(ds[slot]) + acc);
+  }
+}
+
 static int sort_blocks(long long n) {
   long long b = (n + 4 * kSortThreads - 1) / (4 * kSortThreads);
   if (b < 1) b = 1;
@@ -591,6 +669,42 @@ int smoe_cast_f32_to_bf16(const float* src, void* dst, long long n, void* stream
   const long long n8 = n / 8;
   cast_f32_bf16_kernel<<<static_cast<unsigned>((n8 + 255) / 256), 256, 0, S(stream)>>>(
       src, static_cast<__nv_bfloat16*>(dst), n8);
+  return launch_rc();
+}
+
+int smoe_expert_column_sum(const void* src, long long ld, const int* gather_idx, const void* scores,
+                           int scores_dtype, const int* s_scatter_idx, const int* expert_offset, void* out, int E,
+                           int N, void* stream) {
+  if (E <= 0 || N <= 0 || (N % 8) != 0 || (ld % 8) != 0) return SMOE_ERR_SHAPE;
+  const dim3 grid(E, (N + 255) / 256);
+  const __nv_bfloat16* s = static_cast<const __nv_bfloat16*>(src);
+  __nv_bfloat16* o = static_cast<__nv_bfloat16*>(out);
+  if (scores == nullptr || scores_dtype == SMOE_F32)
+    expert_column_sum_kernel<float><<<grid, 256, 0, S(stream)>>>(s, ld, gather_idx, static_cast<const float*>(scores),
+                                                                 s_scatter_idx, expert_offset, o, N);
+  else if (scores_dtype == SMOE_BF16)
+    expert_column_sum_kernel<__nv_bfloat16><<<grid, 256, 0, S(stream)>>>(
+        s, ld, gather_idx, static_cast<const __nv_bfloat16*>(scores), s_scatter_idx, expert_offset, o, N);
+  else
+    return SMOE_ERR_DTYPE;
+  return launch_rc();
+}
+
+int smoe_ds_add_bias_term(const void* dout, const void* b2, const int* expert_offset, const int* x_gather_idx,
+                          const int* s_scatter_idx, void* ds, int ds_dtype, int E, int H, int TK, void* stream) {
+  if (E <= 0 || H <= 0 || (H % 8) != 0 || TK < 0) return SMOE_ERR_SHAPE;
+  if (TK == 0) return SMOE_OK;
+  const unsigned grid = (TK + 7) / 8;
+  const __nv_bfloat16* d = static_cast<const __nv_bfloat16*>(dout);
+  const __nv_bfloat16* b = static_cast<const __nv_bfloat16*>(b2);
+  if (ds_dtype == SMOE_F32)
+    ds_bias_term_kernel<float><<<grid, 256, 0, S(stream)>>>(d, b, expert_offset, x_gather_idx, s_scatter_idx,
+                                                            static_cast<float*>(ds), E, H, TK);
+  else if (ds_dtype == SMOE_BF16)
+    ds_bias_term_kernel<__nv_bfloat16><<<grid, 256, 0, S(stream)>>>(d, b, expert_offset, x_gather_idx, s_scatter_idx,
+                                                                    static_cast<__nv_bfloat16*>(ds), E, H, TK);
+  else
+    return SMOE_ERR_DTYPE;
   return launch_rc();
 }
 

@@ -53,6 +53,11 @@ SIGNATURES: dict[str, tuple] = {
     "smoe_up_projection_backward_dx": (I, [P, P, P, P, I, I, I, I, P, P]),
     "smoe_down_projection_weight_grad": (I, [P, P, P, P, P, I, I, I, I, I, P, P]),
     "smoe_up_projection_weight_grad": (I, [P, P, P, P, P, I, I, I, I, I, P, P]),
+    "smoe_up_projection_forward_act": (I, [P, P, P, P, P, P, P, I, I, I, I, I, I, P, P]),
+    "smoe_down_projection_forward_bias": (I, [P, P, P, P, P, I, I, I, I, P, P]),
+    "smoe_down_projection_backward_dact": (I, [P, P, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, P, P]),
+    "smoe_expert_column_sum": (I, [P, LL, P, P, I, P, P, P, I, I, P]),
+    "smoe_ds_add_bias_term": (I, [P, P, P, P, P, P, I, I, I, I, P]),
     "smoe_fp8_quantize_rows": (I, [P, P, P, LL, I, P]),
     "smoe_fp8_quantize_blocks": (I, [P, P, P, I, I, I, P]),
     "smoe_fp8_up_projection_forward": (I, [P, P, P, P, P, P, P, P, I, I, I, I, I, P, P]),

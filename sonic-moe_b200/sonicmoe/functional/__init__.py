@@ -208,26 +208,41 @@ def _expert_major(w: torch.Tensor) -> torch.Tensor:
     return w.permute(2, 0, 1).contiguous()
 
 
+_ACT_CODE = {ActivationType.SWIGLU: 0, ActivationType.GEGLU: 1, ActivationType.REGLU: 2, ActivationType.RELU_SQ: 3,
+             ActivationType.RELU: 4, ActivationType.GELU: 5, ActivationType.SILU: 6}
+
+
 def _check_experts_args(x, w1, w2, b1, b2, activation_type):
     if (b1 is None) != (b2 is None):
         raise AssertionError("b1 and b2 has to be None or not None at the same time!")
-    if b1 is not None:
-        raise NotImplementedError("expert biases are not implemented by the sm_100a kernels yet")
     if isinstance(activation_type, str):
         activation_type = ActivationType(activation_type)
-    if activation_type != ActivationType.SWIGLU:
-        raise NotImplementedError(f"activation {activation_type} is not implemented by the sm_100a kernels yet")
+    if activation_type not in _ACT_CODE:
+        raise ValueError(f"unknown activation {activation_type}")
     _lib.require_cuda(x, "x")
     if x.dtype != torch.bfloat16 or w1.dtype != torch.bfloat16 or w2.dtype != torch.bfloat16:
         raise TypeError("the sm_100a kernels take bf16 activations and weights "
                         f"(got x {x.dtype}, w1 {w1.dtype}, w2 {w2.dtype})")
     H = x.shape[1]
-    two_i = w1.shape[0]
-    if w1.shape[1] != H or w2.shape[0] != H or w2.shape[1] * 2 != two_i or w1.shape[2] != w2.shape[2]:
+    n1 = w1.shape[0]
+    gated = is_glu(activation_type)
+    if w1.shape[1] != H or w2.shape[0] != H or w2.shape[1] * (2 if gated else 1) != n1 or w1.shape[2] != w2.shape[2]:
         raise ValueError(f"inconsistent shapes: x {tuple(x.shape)}, w1 {tuple(w1.shape)}, w2 {tuple(w2.shape)}")
-    if H % 64 != 0 or (two_i // 2) % 64 != 0:
+    if H % 64 != 0 or w2.shape[1] % 64 != 0:
         raise ValueError("hidden size and intermediate size must be multiples of 64")
+    if (b1 is not None or activation_type != ActivationType.SWIGLU) and n1 % 128 != 0:
+        raise ValueError("with a bias or a non-SwiGLU activation the up projection needs a multiple of 128 output rows")
+    if b1 is not None and (b1.dtype != x.dtype or b2.dtype != x.dtype):
+        raise TypeError("biases must have the activations' dtype")
     return activation_type
+
+
+def _experts(x, w1, b1, w2, b2, scores_flat, route, T, inference, activation_type):
+    """Routed experts: the tuned bias-free SwiGLU kernels, or the general ones for a bias / another activation."""
+    if b1 is None and activation_type == ActivationType.SWIGLU:
+        return _RoutedExperts.apply(x, w1, w2, scores_flat, route, T, inference)
+    return _RoutedExpertsGeneral.apply(x, w1, b1, w2, b2, scores_flat, route, T, inference,
+                                       _ACT_CODE[activation_type])
 
 
 class _RoutedExperts(torch.autograd.Function):
@@ -330,6 +345,109 @@ class _RoutedExperts(torch.autograd.Function):
         return dx, dw1.permute(1, 2, 0), dw2.permute(1, 2, 0), ds, None, None, None
 
 
+class _RoutedExpertsGeneral(torch.autograd.Function):
+    """`_RoutedExperts` with optional expert biases and any activation of ``ActivationType``.
+
+    o[t] = sum score * (W2[e] act(W1[e] x[t] + b1[e]) + b2[e]).  Gradients also for b1, b2; the score gradient
+    gains the term <dout[t], b2[e]>.  Reference: sonicmoe/functional/__init__.py:114-420 with b1/b2 and
+    activation_type, bias kernels sonicmoe/functional/backward.py:36-168.
+    """
+
+    @staticmethod
+    def forward(ctx, x, w1, b1, w2, b2, scores_flat, route: Route, T: int, inference: bool, act: int):
+        dev = x.device
+        x = x.contiguous()
+        w1e = _expert_major(w1)  # (E, N1, H)
+        w2e = _expert_major(w2)  # (E, H, I)
+        E, n1, H = w1e.shape
+        I = w2e.shape[2]
+        TK = route.x_gather_idx.numel()
+        scores_flat = scores_flat.contiguous()
+        b1c = None if b1 is None else b1.contiguous()
+        b2c = None if b2 is None else b2.contiguous()
+        st = _lib.device_state(dev)
+        off = route.expert_frequency_offset.data_ptr()
+        with torch.cuda.device(dev):
+            stream = stream_ptr(dev)
+            z = torch.empty(TK, n1, dtype=x.dtype, device=dev) if not inference else None
+            y1 = torch.empty(TK, I, dtype=x.dtype, device=dev)
+            check(lib.smoe_up_projection_forward_act(
+                x.data_ptr(), w1e.data_ptr(), ptr(b1c), ptr(z), y1.data_ptr(), off, route.x_gather_idx.data_ptr(),
+                T, H, n1, E, TK, act, st.status.data_ptr(), stream), "up_projection_forward_act")
+            y2 = torch.empty(TK, H, dtype=x.dtype, device=dev)
+            check(lib.smoe_down_projection_forward_bias(
+                y1.data_ptr(), w2e.data_ptr(), ptr(b2c), y2.data_ptr(), off, H, I, E, TK, st.status.data_ptr(),
+                stream), "down_projection_forward_bias")
+            o = torch.empty(T, H, dtype=x.dtype, device=dev)
+            check(lib.smoe_gather_sum(
+                y2.data_ptr(), o.data_ptr(), scores_flat.data_ptr(), _lib.dtype_code(scores_flat.dtype),
+                route.s_reverse_scatter_idx.data_ptr(), ptr(route.token_offset), T, H, max(route.K, 1), stream),
+                "gather_sum")
+        if not inference:
+            ctx.save_for_backward(x, w1e, w2e, z, scores_flat, b2c)
+            ctx.route = route
+            ctx.dims = (T, H, I, E, TK, n1)
+            ctx.act = act
+            ctx.has_bias = b1 is not None
+        return o
+
+    @staticmethod
+    def backward(ctx, dout):
+        x, w1e, w2e, z, scores_flat, b2c = ctx.saved_tensors
+        route: Route = ctx.route
+        T, H, I, E, TK, n1 = ctx.dims
+        dev = x.device
+        dout = dout.contiguous().to(x.dtype)
+        st = _lib.device_state(dev)
+        off = route.expert_frequency_offset.data_ptr()
+        gat = route.x_gather_idx.data_ptr()
+        sct = route.s_scatter_idx.data_ptr()
+        sc_bf16 = int(scores_flat.dtype == torch.bfloat16)
+        with torch.cuda.device(dev):
+            stream = stream_ptr(dev)
+            dz = torch.empty(TK, n1, dtype=x.dtype, device=dev)
+            y1s = torch.empty(TK, I, dtype=x.dtype, device=dev)
+            ncols = lib.smoe_ds_partial_columns(I)
+            ds_partial = torch.empty(ncols, TK, dtype=torch.float32, device=dev)
+            check(lib.smoe_down_projection_backward_dact(
+                dout.data_ptr(), w2e.data_ptr(), z.data_ptr(), scores_flat.data_ptr(), sc_bf16, dz.data_ptr(),
+                y1s.data_ptr(), ds_partial.data_ptr(), off, gat, sct, T, H, I, E, TK, ctx.act, st.status.data_ptr(),
+                stream), "down_projection_backward_dact")
+            ds = torch.empty_like(scores_flat)
+            check(lib.smoe_ds_reduce(ds_partial.data_ptr(), sct, ds.data_ptr(), _lib.dtype_code(ds.dtype), TK, ncols,
+                                     stream), "ds_reduce")
+            db1 = db2 = None
+            if ctx.has_bias:
+                check(lib.smoe_ds_add_bias_term(dout.data_ptr(), b2c.data_ptr(), off, gat, sct, ds.data_ptr(),
+                                                _lib.dtype_code(ds.dtype), E, H, TK, stream), "ds_add_bias_term")
+                db2 = torch.empty(E, H, dtype=x.dtype, device=dev)
+                check(lib.smoe_expert_column_sum(dout.data_ptr(), H, gat, scores_flat.data_ptr(),
+                                                 _lib.dtype_code(scores_flat.dtype), sct, off, db2.data_ptr(), E, H,
+                                                 stream), "expert_column_sum")
+                db1 = torch.empty(E, n1, dtype=x.dtype, device=dev)
+                check(lib.smoe_expert_column_sum(dz.data_ptr(), n1, None, None, 0, None, off, db1.data_ptr(), E, n1,
+                                                 stream), "expert_column_sum")
+            dw2 = torch.empty_like(w2e)
+            check(lib.smoe_down_projection_weight_grad(
+                dout.data_ptr(), y1s.data_ptr(), dw2.data_ptr(), off, gat, T, H, I, E, TK, st.status.data_ptr(),
+                stream), "down_projection_weight_grad")
+            # the two kernels below take the up projection's output rows as 2 * (their I argument)
+            half = n1 // 2
+            dw1 = torch.empty_like(w1e)
+            check(lib.smoe_up_projection_weight_grad(
+                x.data_ptr(), dz.data_ptr(), dw1.data_ptr(), off, gat, T, H, half, E, TK, st.status.data_ptr(),
+                stream), "up_projection_weight_grad")
+            dx_expanded = torch.empty(TK, H, dtype=x.dtype, device=dev)
+            check(lib.smoe_up_projection_backward_dx(
+                dz.data_ptr(), w1e.data_ptr(), dx_expanded.data_ptr(), off, H, half, E, TK, st.status.data_ptr(),
+                stream), "up_projection_backward_dx")
+            dx = torch.empty(T, H, dtype=x.dtype, device=dev)
+            check(lib.smoe_gather_sum(
+                dx_expanded.data_ptr(), dx.data_ptr(), None, _lib.SMOE_F32, route.s_reverse_scatter_idx.data_ptr(),
+                ptr(route.token_offset), T, H, max(route.K, 1), stream), "gather_sum")
+        return dx, dw1.permute(1, 2, 0), db1, dw2.permute(1, 2, 0), db2, ds, None, None, None, None
+
+
 def moe_TC_softmax_topk_layer(
     x: torch.Tensor,
     router_w: torch.Tensor,
@@ -348,13 +466,13 @@ def moe_TC_softmax_topk_layer(
     (E,2I,H) / (E,H,I) parameters, gate/up rows of w1 interleaved.
     Reference: sonicmoe/functional/__init__.py:423-490.
     """
-    _check_experts_args(x, w1, w2, b1, b2, activation_type)
+    activation_type = _check_experts_args(x, w1, w2, b1, b2, activation_type)
     E = router_w.size(0)
     T = x.size(0)
     # a router kept in fp32 (an extension over the reference) computes its logits in fp32
     router_logits = F.linear(x if x.dtype == router_w.dtype else x.to(router_w.dtype), router_w)
     inference = is_inference_mode_enabled or not torch.is_grad_enabled()
-    if torch.compiler.is_compiling():
+    if torch.compiler.is_compiling() and b1 is None and activation_type == ActivationType.SWIGLU:
         # opaque custom ops instead of autograd functions with ctypes calls inside (torch.compile, fullgraph)
         from .compiled_ops import layer_with_custom_ops
 
@@ -362,7 +480,7 @@ def moe_TC_softmax_topk_layer(
         return o, router_logits, freq
     scores, indices = topk_softmax(router_logits, K)
     route = _route_metadata(indices.reshape(-1), None, E, K)
-    o = _RoutedExperts.apply(x, w1, w2, scores.reshape(-1), route, T, inference)
+    o = _experts(x, w1, b1, w2, b2, scores.reshape(-1), route, T, inference, activation_type)
     return o, router_logits, route.expert_frequency
 
 
@@ -385,12 +503,12 @@ def moe_general_routing_inputs(
     Returns (o (T,H), expert_frequency (E,) int32).  Gradients flow to x, w1, w2 and router_scores.
     Reference: sonicmoe/functional/__init__.py:497-562.
     """
-    _check_experts_args(x, w1, w2, b1, b2, activation_type)
+    activation_type = _check_experts_args(x, w1, w2, b1, b2, activation_type)
     T = x.size(0)
     E = w2.size(-1)
     tok = token_indices.contiguous().to(torch.int32)
     route = _route_metadata(expert_indices, tok, E, 0)
     route.token_offset = _sorted_offsets(tok, T)
     inference = is_inference_mode_enabled or not torch.is_grad_enabled()
-    o = _RoutedExperts.apply(x, w1, w2, router_scores, route, T, inference)
+    o = _experts(x, w1, b1, w2, b2, router_scores, route, T, inference, activation_type)
     return o, route.expert_frequency

@@ -71,7 +71,9 @@ def test_cuda_backend_refuses_cpu_and_unsupported_inputs(built_library):
     w2 = m.c_proj.weight.permute(1, 2, 0)
     with pytest.raises(AssertionError):
         moe_TC_softmax_topk_layer(inp["x"], m.router.weight, w1, torch.zeros(8, 128), w2, None, 2)
-    with pytest.raises(NotImplementedError):
+    with pytest.raises(ValueError):
+        moe_TC_softmax_topk_layer(inp["x"], m.router.weight, w1, None, w2, None, 2, 0, "not-an-activation")
+    with pytest.raises(_lib.SonicMoEError):  # a supported activation still has no CPU path
         moe_TC_softmax_topk_layer(inp["x"], m.router.weight, w1, None, w2, None, 2, 0, "gelu")
     with pytest.raises(ValueError):
         m(inp["x"], kernel_backend_moe=__import__("sonicmoe").KernelBackendMoE.scattermoe)

@@ -230,3 +230,47 @@ def test_torch_compile_fullgraph_matches_eager(built_library):
     assert rel(aux, aux_ref) < 1e-5
     for a, b in zip(g, g_ref):
         assert a.shape == b.shape and rel(a, b) < 1e-3
+
+
+@pytest.mark.parametrize("act,bias", [("swiglu", True), ("geglu", False), ("reglu", True), ("gelu", True),
+                                      ("relu", False), ("silu", True), ("relu_sq", False)])
+def test_bias_and_activations_vs_oracle(built_library, act, bias):
+    """Every activation of the layer, with and without expert biases (the reference test matrix has
+    add_bias, tests/moe_test.py:25-56; activations are a benchmark flag, benchmarks/moe-cute.py:62-94)."""
+    import sonicmoe
+    from sonicmoe import _lib
+    from sonicmoe.enums import ActivationType, is_glu
+
+    T, H, I, E, K = 700, 256, 128, 8, 2
+    kind = ActivationType(act)
+    n1 = 2 * I if is_glu(kind) else I
+    g = torch.Generator().manual_seed(len(act) + bias)
+    m = sonicmoe.MoE(E, K, H, I, kind, bias, 0.05).cuda().to(torch.bfloat16)
+    with torch.no_grad():
+        m.router.weight.copy_(torch.randn(E, H, generator=g) * 0.05)
+        if bias:
+            m.c_fc.bias.copy_(torch.randn(E, n1, generator=g) * 0.1)
+            m.c_proj.bias.copy_(torch.randn(E, H, generator=g) * 0.1)
+    x = torch.randn(T, H, generator=g).bfloat16().cuda().requires_grad_(True)
+    dout = torch.randn(T, H, generator=g).bfloat16().cuda()
+    o, _aux = m(x)
+    params = [m.c_fc.weight, m.c_proj.weight] + ([m.c_fc.bias, m.c_proj.bias] if bias else [])
+    grads = torch.autograd.grad(o, [x] + params, dout)
+    torch.cuda.synchronize()
+    _lib.check_status()
+
+    logits = torch.nn.functional.linear(x.detach(), m.router.weight.detach()).float().cpu()
+    scores, idx = orc.topk_softmax(logits, K)
+    route = orc.route_metadata(idx, E, T, K=K)
+    f = lambda t: None if t is None else t.detach().float().cpu()
+    ref = orc.experts_autograd(f(x), f(m.c_fc.weight), f(m.c_fc.bias), f(m.c_proj.weight), f(m.c_proj.bias),
+                               scores.reshape(-1), route, act, f(dout))
+    dlogits = orc.softmax_topk_backward(scores, idx, ref["ds"].reshape(T, K), E)
+    dx_ref = ref["dx"] + dlogits @ f(m.router.weight)
+    assert rel(o, ref["o"]) < TOL
+    assert rel(grads[0], dx_ref) < TOL
+    assert rel(grads[1], ref["dw1"]) < TOL
+    assert rel(grads[2], ref["dw2"]) < TOL
+    if bias:
+        assert rel(grads[3], ref["db1"]) < TOL
+        assert rel(grads[4], ref["db2"]) < TOL
