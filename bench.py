@@ -404,18 +404,87 @@ def run_gpu_arm(args, rank, world, local_rank):
 
 
 EP_CFG = dict(T=65536, H=2048, I=768, E=64, K=4)  # BASELINE configs[4]: tokens per GPU, Zipf-skewed routing
+EP_FP8_CFG = dict(T=16384, H=7168, I=2048, E=256, K=8)  # BASELINE configs[3]: tokens per GPU, FP8 experts
+ROUNDING_CFG = dict(T=16384, H=4096, I=1024, E=256, K=8)  # BASELINE configs[2]: token rounding to multiples of 128
 
 
-def run_ep_arm(args, rank, world, local_rank):
-    """Expert-parallel, load-skewed layer (BASELINE configs[4]): T=65536 tokens per GPU, H=2048, I=768, E=64,
-    K=4, router logits biased by 2*log(1/rank_e) with a seeded permutation of expert ranks; experts sharded
-    over the ranks, dispatch/combine by NCCL all-to-all.  Not the default workload: `--workload ep_zipf`."""
+def run_rounding_arm(args, local_rank):
+    """Token-rounding routing (BASELINE configs[2]): T=16384, H=4096, I=1024, E=256, K=8; after top-K every expert's
+    token count is rounded to the nearest multiple of 128.  As in the reference's benchmark
+    (benchmarks/moe-token-rounding.py:355-455) the timed region is the routed layer forward + backward on
+    precomputed routing; the router's own time is reported beside it.  FLOPs use the realised pair count."""
+    from sonicmoe import _lib
+    from sonicmoe.enums import ActivationType
+    from sonicmoe.functional import forward_token_choice_rounding, moe_general_routing_inputs
+
+    cfg = ROUNDING_CFG
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    T, H, I, E, K = (cfg[k] for k in "THIEK")
+    g = torch.Generator(device=dev).manual_seed(0)
+    router_w = (torch.randn(E, H, generator=g, device=dev) * 0.02).bfloat16()
+    w1 = (torch.randn(E, 2 * I, H, generator=g, device=dev) * 0.02).bfloat16().requires_grad_(True)
+    w2 = (torch.randn(E, H, I, generator=g, device=dev) * 0.02).bfloat16().requires_grad_(True)
+    x = torch.randn(T, H, generator=g, device=dev).bfloat16().requires_grad_(True)
+    dout = torch.randn(T, H, generator=g, device=dev).bfloat16()
+
+    def route():
+        with torch.no_grad():
+            return forward_token_choice_rounding(x.detach(), router_w, E, K, 128, "nr")
+
+    scores, tokens, experts = route()
+    scores = scores.detach().requires_grad_(True)
+    params = [x, scores, w1, w2]
+
+    def step():
+        for p_ in params:
+            p_.grad = None
+        o, _freq = moe_general_routing_inputs(x, scores, tokens, experts, w1.permute(1, 2, 0), None,
+                                              w2.permute(1, 2, 0), None, E, 0, ActivationType.SWIGLU)
+        o.backward(dout)
+
+    def timed(fn, n):
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / n
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    ms = timed(step, args.steps)
+    route_ms = timed(route, 3)
+    _lib.check_status(dev)
+    pairs = tokens.numel()
+    counts = torch.bincount(experts.long(), minlength=E)
+    value = 18.0 * pairs * I * H / (ms * 1e-3) / 1e12
+    print(json.dumps({
+        "metric": "moe_fwd_bwd_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "tokens_per_s": T / (ms * 1e-3),
+        "config": {"workload": "moe_layer_fwd_bwd_token_rounding_nr128_T16384_H4096_I1024_E256_K8", **cfg,
+                   "routing": "token choice top-K, per-expert count rounded to the nearest multiple of 128"},
+        "routed_pairs": pairs, "pairs_vs_topk": pairs / (T * K), "router_ms": route_ms,
+        "all_counts_multiple_of_128": bool((counts % 128 == 0).all().item()),
+    }), flush=True)
+
+
+def run_ep_arm(args, rank, world, local_rank, fp8=False):
+    """Expert-parallel layer, experts sharded over the ranks, dispatch/combine by NCCL all-to-all.
+    `--workload ep_zipf` (BASELINE configs[4]): T=65536 tokens per GPU, H=2048, I=768, E=64, K=4, router logits
+    biased by 2*log(1/rank_e) with a seeded permutation of expert ranks.  `--workload ep_fp8` (BASELINE
+    configs[3]): T=16384 per GPU, H=7168, I=2048, E=256, K=8, expert GEMMs of forward and activation gradients in
+    FP8 E4M3 with 1x128 / 128x128 block scales (weight gradients bf16)."""
     import torch.distributed as dist
 
     from sonicmoe import _lib
-    from sonicmoe.expert_parallel import moe_ep_softmax_topk_layer
+    from sonicmoe.expert_parallel import Fp8CudaOps, moe_ep_softmax_topk_layer
 
-    cfg = EP_CFG
+    cfg = EP_FP8_CFG if fp8 else EP_CFG
+    ops = Fp8CudaOps() if fp8 else None
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
     dist.init_process_group("nccl", device_id=dev)
@@ -424,7 +493,7 @@ def run_ep_arm(args, rank, world, local_rank):
     g = torch.Generator(device=dev).manual_seed(0)
     router_w = (torch.randn(E, H, generator=g, device=dev) * 0.02).bfloat16().requires_grad_(True)
     ranks = torch.randperm(E, generator=g, device=dev) + 1
-    logit_bias = 2.0 * torch.log(1.0 / ranks.float())
+    logit_bias = None if fp8 else 2.0 * torch.log(1.0 / ranks.float())
     g = torch.Generator(device=dev).manual_seed(1 + rank)
     w1 = (torch.randn(e_local, 2 * I, H, generator=g, device=dev) * 0.02).bfloat16().requires_grad_(True)
     w2 = (torch.randn(e_local, H, I, generator=g, device=dev) * 0.02).bfloat16().requires_grad_(True)
@@ -436,7 +505,7 @@ def run_ep_arm(args, rank, world, local_rank):
     def step():
         for p_ in params:
             p_.grad = None
-        o, _logits, freq = moe_ep_softmax_topk_layer(x, router_w, w1, w2, K, E, logit_bias=logit_bias)
+        o, _logits, freq = moe_ep_softmax_topk_layer(x, router_w, w1, w2, K, E, logit_bias=logit_bias, ops=ops)
         o.backward(dout)
         stats["freq"] = freq
 
@@ -468,10 +537,12 @@ def run_ep_arm(args, rank, world, local_rank):
         line = {
             "metric": "moe_fwd_bwd_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "vs_baseline": None, "dtype": "fp8_e4m3 (weight gradients bf16)" if fp8 else "bf16", "data": "synthetic",
             "tokens_per_s": world * T / (ms_per_step * 1e-3), "tflops_per_gpu": value / world,
-            "config": {"workload": "moe_layer_fwd_bwd_expert_parallel_zipf_T65536_per_gpu_H2048_I768_E64_K4", **cfg,
-                       "parallelism": f"ep{world}", "routing": "softmax_topk + per-expert logit bias 2*log(1/rank)"},
+            "config": {"workload": ("moe_layer_fwd_bwd_expert_parallel_fp8_T16384_per_gpu_H7168_I2048_E256_K8" if fp8 else
+                                    "moe_layer_fwd_bwd_expert_parallel_zipf_T65536_per_gpu_H2048_I768_E64_K4"), **cfg,
+                       "parallelism": f"ep{world}",
+                       "routing": "softmax_topk" if fp8 else "softmax_topk + per-expert logit bias 2*log(1/rank)"},
             "expert_load_max_over_mean": (freq.max() / freq.mean()).item(),
             "rank_load_max_over_mean": (per_rank_rows.max() / per_rank_rows.mean()).item(),
         }
@@ -491,7 +562,7 @@ def main():
     ap.add_argument("--tokens", type=int, default=CFG["T"])
     ap.add_argument("--experts", type=int, default=CFG["E"])
     ap.add_argument("--reps", type=int, default=5)
-    ap.add_argument("--workload", default="topk", choices=["topk", "ep_zipf"])
+    ap.add_argument("--workload", default="topk", choices=["topk", "ep_zipf", "ep_fp8", "token_rounding"])
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -501,12 +572,15 @@ def main():
         return
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the layer has no CPU path (use --impl reference for the CPU arm)")
-    if args.workload == "ep_zipf":
+    if args.workload == "token_rounding":
+        run_rounding_arm(args, local_rank)
+        return
+    if args.workload in ("ep_zipf", "ep_fp8"):
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         os.environ.setdefault("MASTER_PORT", "29541")
         os.environ.setdefault("RANK", "0")
         os.environ.setdefault("WORLD_SIZE", "1")
-        run_ep_arm(args, rank, world, local_rank)
+        run_ep_arm(args, rank, world, local_rank, fp8=args.workload == "ep_fp8")
         return
     if args.kernels_only:
         cfg = dict(CFG, T=args.tokens, E=args.experts)

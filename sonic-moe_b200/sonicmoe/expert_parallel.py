@@ -80,6 +80,20 @@ class CudaOps:
         return fn._RoutedExperts.apply(x_rows, w1.permute(1, 2, 0), w2.permute(1, 2, 0), scores, route, R, inference)
 
 
+class Fp8CudaOps(CudaOps):
+    """As CudaOps, with the local experts' forward and activation-gradient GEMMs in FP8 (E4M3, block scales)."""
+
+    def local_experts(self, x_rows, w1, w2, scores, local_expert, num_local_experts, inference):
+        from . import functional as fn
+        from .functional.fp8 import _RoutedExpertsFp8
+
+        R = x_rows.shape[0]
+        rows = torch.arange(R, dtype=torch.int32, device=x_rows.device)
+        route = fn._route_metadata(local_expert, rows, num_local_experts, 0)
+        route.K = 1
+        return _RoutedExpertsFp8.apply(x_rows, w1.permute(1, 2, 0), w2.permute(1, 2, 0), scores, route, R, inference)
+
+
 class _GatherRows(torch.autograd.Function):
     """out[r] = x[x_gather_idx[r]] (grouped order); backward: dx[t] = sum of the K rows routed from token t."""
 

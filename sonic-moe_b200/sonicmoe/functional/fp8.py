@@ -83,14 +83,15 @@ class _RoutedExpertsFp8(torch.autograd.Function):
                 route.s_reverse_scatter_idx.data_ptr(), ptr(route.token_offset), T, H, max(route.K, 1), stream),
                 "gather_sum")
         if not inference:
-            ctx.save_for_backward(x, w1e, w2e, z, scores_flat)
+            # the quantised weights are kept for the backward pass (1 byte per weight) instead of being rebuilt
+            ctx.save_for_backward(x, w1e, w2e, z, scores_flat, w1q, w1s, w2q, w2s)
             ctx.route = route
             ctx.dims = (T, H, I, E, TK)
         return o
 
     @staticmethod
     def backward(ctx, dout):
-        x, w1e, w2e, z, scores_flat = ctx.saved_tensors
+        x, w1e, w2e, z, scores_flat, w1q, w1s, w2q, w2s = ctx.saved_tensors
         route = ctx.route
         T, H, I, E, TK = ctx.dims
         dev = x.device
@@ -99,8 +100,6 @@ class _RoutedExpertsFp8(torch.autograd.Function):
         off = route.expert_frequency_offset.data_ptr()
         gat = route.x_gather_idx.data_ptr()
         doutq, douts = quantize_rows(dout)
-        w1q, w1s = quantize_blocks(w1e)
-        w2q, w2s = quantize_blocks(w2e)
         with torch.cuda.device(dev):
             stream = stream_ptr(dev)
             dz = torch.empty(TK, 2 * I, dtype=x.dtype, device=dev)
