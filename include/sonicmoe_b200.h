@@ -100,6 +100,23 @@ int smoe_route_metadata(const int* expert_idx, const int* token_idx, long long n
  * (sonicmoe/functional/__init__.py:66-73). */
 int smoe_sorted_offsets(const int* sorted_idx, long long n, int T, int* offsets, void* stream);
 
+/* Token rounding: after the top-K choice, round every expert's token count to a multiple of `tile`
+ * (SMOE_ROUND_DOWN floor, SMOE_ROUND_UP ceil, SMOE_ROUND_NEAREST nearest with ties to even, each capped at T) by
+ * dropping the expert's lowest-ranked top-K tokens or admitting its best-ranked other tokens.  Ranking of the
+ * tokens of one expert: tokens whose top-K holds the expert, by score; then the others by (score - 1), rounded in
+ * the scores' dtype; equal values by lower token id.
+ * scores (T,E) [SMOE_F32 or SMOE_BF16]: probabilities with the top-K entries already renormalised; topk_idx (T,K).
+ * Outputs: expert_count (E) = rounded counts; the kept pairs as tokens / experts (ascending token, ascending
+ * expert within a token), at most `capacity` of them written; num_pairs (1) = their number (sum of expert_count).
+ * workspace: smoe_token_rounding_workspace_bytes(T,E) bytes, 16-byte aligned.
+ * Replaces the ranking matrix, the argsort over tokens, the count mask and the final argsort of
+ * forward_token_choice_rounding (benchmarks/moe-token-rounding.py:153-191), whose tie order is unspecified. */
+enum { SMOE_ROUND_DOWN = 0, SMOE_ROUND_UP = 1, SMOE_ROUND_NEAREST = 2 };
+size_t smoe_token_rounding_workspace_bytes(int T, int E);
+int smoe_token_rounding_select(const void* scores, int scores_dtype, const int* topk_idx, int T, int E, int K,
+                               int tile, int mode, int* expert_count, int* tokens, int* experts, int* num_pairs,
+                               int capacity, void* workspace, void* stream);
+
 /* out[t,:] = sum over p in [token_offset[t], token_offset[t+1]) (or [t*K, (t+1)*K) when token_offset is
  * NULL) of weights[p] * src[reverse_idx[p], :]; weights NULL = 1, else SMOE_F32 / SMOE_BF16; src, out
  * bf16 with H columns; fp32 accumulation.  Replaces sonicmoe::_router_forward and

@@ -42,6 +42,8 @@ SIGNATURES: dict[str, tuple] = {
     "smoe_route_metadata_workspace_bytes": (c_size_t, [I]),
     "smoe_route_metadata": (I, [P, P, LL, I, I, P, P, P, P, P, P, P]),
     "smoe_sorted_offsets": (I, [P, LL, I, P, P]),
+    "smoe_token_rounding_workspace_bytes": (c_size_t, [I, I]),
+    "smoe_token_rounding_select": (I, [P, I, P, I, I, I, I, I, P, P, P, P, I, P, P]),
     "smoe_gather_sum": (I, [P, P, P, I, P, P, I, I, I, P]),
     "smoe_cast_f32_to_bf16": (I, [P, P, LL, P]),
     "smoe_ds_reduce": (I, [P, P, P, I, I, I, P]),

@@ -90,13 +90,13 @@ def test_rounded_counts():
     assert torch.equal(rounded_counts(f, "nr"), orc.rounded_counts(f, "nr"))
 
 
-def test_token_rounding_router_matches_oracle_on_cpu():
-    """The router is device-agnostic torch code; on CPU it must agree with the oracle bit for bit."""
-    from sonicmoe.functional.token_rounding import forward_token_choice_rounding
+def test_token_rounding_router_has_no_cpu_path():
+    """The selection runs in the library's CUDA kernels only: CPU tensors are refused, unknown modes too."""
+    from sonicmoe import _lib
+    from sonicmoe.functional.token_rounding import forward_token_choice_rounding, select_pairs
 
-    for dtype in (torch.float32, torch.bfloat16):
-        inp = orc.make_inputs(512, 64, 64, 8, 2, seed=11, dtype=dtype)
-        s, tok, exp = forward_token_choice_rounding(inp["x"], inp["router_w"], 8, 2, 128, "nr")
-        logits = torch.nn.functional.linear(inp["x"], inp["router_w"])
-        s_ref, tok_ref, exp_ref, _ = orc.token_rounding_route(logits, 2, "nr", dtype)
-        assert torch.equal(tok, tok_ref) and torch.equal(exp, exp_ref) and torch.equal(s, s_ref)
+    inp = orc.make_inputs(512, 64, 64, 8, 2, seed=11, dtype=torch.float32)
+    with pytest.raises(_lib.SonicMoEError):
+        forward_token_choice_rounding(inp["x"], inp["router_w"], 8, 2, 128, "nr")
+    with pytest.raises(NotImplementedError):
+        select_pairs(torch.zeros(4, 8), torch.zeros(4, 2, dtype=torch.int32), "sideways")

@@ -132,6 +132,48 @@ def test_route_metadata_general_bit_exact(smoe, T, E, n):
 
 
 # ---------------------------------------------------------------------------------------------------
+# token rounding
+# ---------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("routing", ["nr", "up", "down"])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("T,E,K", [(1024, 8, 2), (2048, 16, 4), (1000, 24, 3), (4096, 256, 8), (130, 300, 2), (64, 4, 1)])
+def test_token_rounding_selection_bit_exact(smoe, T, E, K, dtype, routing):
+    """Kept (token, expert) pairs, their order, the scores and the rounded counts against the oracle's full sorts.
+    bf16 scores tie massively after the "-1" shift, so the lower-token-first rule is exercised on every expert;
+    T = 1000 and 130 are not multiples of 32 or of the tile (counts are capped at T)."""
+    _lib, fn = smoe
+    from sonicmoe.functional.token_rounding import select_pairs, topk_indices
+
+    g = torch.Generator().manual_seed(T * 3 + E + K)
+    logits = torch.randn(T, E, generator=g) * 2.0
+    s_ref, t_ref, e_ref, score_matrix = orc.token_rounding_route(logits, K, routing, dtype)
+    probs = torch.softmax(logits.float(), dim=-1).to(dtype)
+    topk = topk_indices(probs.cuda(), K)
+    assert torch.equal(topk.cpu().long(), probs.sort(dim=-1, descending=True, stable=True).indices[:, :K])
+    tokens, experts, count = select_pairs(score_matrix.cuda(), topk, routing)
+    assert torch.equal(tokens.cpu(), t_ref) and torch.equal(experts.cpu(), e_ref)
+    freq = torch.bincount(topk.cpu().long().reshape(-1), minlength=E)
+    want = orc.rounded_counts(freq, routing).clamp(max=T)
+    assert torch.equal(count.cpu(), want.int())
+    assert torch.equal(torch.bincount(e_ref.long(), minlength=E).int(), want.int())
+    assert torch.equal(score_matrix[tokens.cpu().long(), experts.cpu().long()], s_ref)
+
+
+def test_token_rounding_selection_all_ties(smoe):
+    """Every score equal: the top-K goes to the lowest expert ids and every cut keeps the lowest token ids."""
+    _lib, fn = smoe
+    from sonicmoe.functional.token_rounding import select_pairs, topk_indices
+
+    T, E, K = 700, 8, 2
+    logits = torch.zeros(T, E)
+    for routing in ("nr", "up", "down"):
+        s_ref, t_ref, e_ref, score_matrix = orc.token_rounding_route(logits, K, routing, torch.bfloat16)
+        topk = topk_indices(torch.softmax(logits, -1).bfloat16().cuda(), K)
+        tokens, experts, count = select_pairs(score_matrix.cuda(), topk, routing)
+        assert torch.equal(tokens.cpu(), t_ref) and torch.equal(experts.cpu(), e_ref)
+
+
+# ---------------------------------------------------------------------------------------------------
 # grouped GEMMs and reductions, one entry point at a time
 # ---------------------------------------------------------------------------------------------------
 SHAPES = [
