@@ -257,6 +257,33 @@ int smoe_fp8_up_projection_backward_dx(const void* dzq, const float* dz_scale, c
                                        void* dx_expanded, const int* expert_offset, int H, int I, int E, int TK,
                                        int* status, void* stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * FP8 (E4M3) path with power-of-two block scales in UE8M0 (one byte = exponent + 127), applied by the tensor
+ * cores' own block scaling (tcgen05.mma kind::mxf8f6f4.block_scale) instead of in software.  Same block shapes
+ * as above; scale = the smallest power of two >= amax / 448 (2^0 for an all-zero block).  Activation scales are
+ * (rows, smoe_mxfp8_scale_row_bytes(cols)) bytes: byte b of a row belongs to columns [128 b, 128 b + 128), rows
+ * padded to whole 32-bit words (4-byte aligned base).  Weight scales are (batch, ceil(rows/128), cols/128) bytes.
+ * The GEMM entry points take the same arguments as their smoe_fp8_* namesakes.  No reference counterpart.
+ * ------------------------------------------------------------------------------------------- */
+int smoe_mxfp8_scale_row_bytes(int cols);
+int smoe_mxfp8_quantize_rows(const void* x, void* q, void* scale, long long rows, int cols, void* stream);
+int smoe_mxfp8_quantize_blocks(const void* w, void* q, void* scale, int batch, int rows, int cols, void* stream);
+int smoe_mxfp8_up_projection_forward(const void* xq, const void* x_scale, const void* w1q, const void* w1_scale,
+                                     void* z, void* y1, const int* expert_offset, const int* x_gather_idx, int T,
+                                     int H, int I, int E, int TK, int* status, void* stream);
+int smoe_mxfp8_down_projection_forward(const void* y1q, const void* y1_scale, const void* w2q, const void* w2_scale,
+                                       void* y2, const int* expert_offset, int H, int I, int E, int TK, int* status,
+                                       void* stream);
+int smoe_mxfp8_down_projection_backward_act(const void* doutq, const void* dout_scale, const void* w2q,
+                                            const void* w2_scale, const void* z, const void* scores,
+                                            int scores_are_bf16, void* dz, void* y1s, float* ds_partial,
+                                            const int* expert_offset, const int* x_gather_idx,
+                                            const int* s_scatter_idx, int T, int H, int I, int E, int TK, int* status,
+                                            void* stream);
+int smoe_mxfp8_up_projection_backward_dx(const void* dzq, const void* dz_scale, const void* w1q, const void* w1_scale,
+                                         void* dx_expanded, const int* expert_offset, int H, int I, int E, int TK,
+                                         int* status, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

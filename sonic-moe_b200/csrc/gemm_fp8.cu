@@ -1,5 +1,7 @@
-// FP8 (E4M3, fp32 block scales) entry points: quantisation kernels and the launchers of the FP8 grouped GEMMs.
+// FP8 (E4M3) entry points: quantisation kernels and the launchers of the FP8 grouped GEMMs, for fp32 block
+// scales (amax / 448, applied in software) and for power-of-two UE8M0 block scales (applied by the tensor cores).
 #include "gemm_fp8.cuh"
+#include "gemm_mxfp8.cuh"
 
 #include <cuda_fp8.h>
 
@@ -60,13 +62,11 @@ static int num_sms() {
   return sms;
 }
 
-template <bool A_GATHER, bool B_MN, int EPI>
-static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, const Scales& sc,
-                  cudaStream_t stream) {
-  auto kernel = grouped_gemm_fp8_kernel<A_GATHER, B_MN, EPI>;
-  static bool configured = false;
+template <class Kernel, class ScaleArgs>
+static int launch_kernel(Kernel kernel, bool& configured, int smem_bytes, const CUtensorMap& tmA,
+                         const CUtensorMap& tmB, const GemmParams& p, const ScaleArgs& sc, cudaStream_t stream) {
   if (!configured) {
-    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) != cudaSuccess)
       return SMOE_ERR_LAUNCH;
     configured = true;
   }
@@ -75,7 +75,7 @@ static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmPara
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(sms & ~1), 1, 1);
   cfg.blockDim = dim3(THREADS, 1, 1);
-  cfg.dynamicSmemBytes = SMEM_BYTES;
+  cfg.dynamicSmemBytes = smem_bytes;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -87,6 +87,21 @@ static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmPara
   return cudaLaunchKernelEx(&cfg, kernel, tmA, tmB, p, sc) == cudaSuccess ? SMOE_OK : SMOE_ERR_LAUNCH;
 }
 
+template <bool A_GATHER, bool B_MN, int EPI>
+static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, const Scales& sc,
+                  cudaStream_t stream) {
+  static bool configured = false;
+  return launch_kernel(grouped_gemm_fp8_kernel<A_GATHER, B_MN, EPI>, configured, SMEM_BYTES, tmA, tmB, p, sc, stream);
+}
+
+template <bool A_GATHER, bool B_MN, int EPI>
+static int launch_mx(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, const mx8::ScaleBytes& sc,
+                     cudaStream_t stream) {
+  static bool configured = false;
+  return launch_kernel(mx8::grouped_gemm_mxfp8_kernel<A_GATHER, B_MN, EPI>, configured, mx8::SMEM_BYTES, tmA, tmB, p,
+                       sc, stream);
+}
+
 static bool bad_shape(int H, int I, int E) {
   return H <= 0 || I <= 0 || E <= 0 || E > MAX_EXPERTS || (H % 128) != 0 || (I % 128) != 0;
 }
@@ -94,6 +109,46 @@ static bool bad_shape(int H, int I, int E) {
 // ---- quantisation ------------------------------------------------------------------------------------
 __device__ __forceinline__ uint8_t to_e4m3(float v) {
   return static_cast<uint8_t>(__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3));
+}
+
+// Power-of-two scale: the smallest 2^e >= amax / 448, as the UE8M0 byte e + 127 and the exact factor 2^-e.
+__device__ __forceinline__ uint8_t pow2_scale(float amax, float& inv_scale) {
+  int e = 0;
+  if (amax > 0.f) {
+    const float m = frexpf(amax / 448.f, &e);  // amax / 448 = m 2^e, m in [0.5, 1)
+    if (m == 0.5f) --e;
+    e = max(e, -127);
+  }
+  inv_scale = __int_as_float((127 - e) << 23);  // e <= 121 for finite bf16 inputs
+  return static_cast<uint8_t>(e + 127);
+}
+
+// One warp per (row, 128-column block): power-of-two scale byte at scale[row * ld + block] (ld = blocks per row
+// rounded up to 4; the padding bytes are 2^0), q = x * 2^-e.
+__global__ void __launch_bounds__(256) quantize_rows_pow2_kernel(const __nv_bfloat16* __restrict__ x,
+                                                                 uint8_t* __restrict__ q, uint8_t* __restrict__ scale,
+                                                                 long long rows, int cols, int ld) {
+  const long long w = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (w >= rows * ld) return;
+  const int lane = threadIdx.x & 31;
+  const long long row = w / ld;
+  const int cb = static_cast<int>(w % ld);
+  if (cb >= (cols >> 7)) {
+    if (lane == 0) scale[row * ld + cb] = 0x7F;
+    return;
+  }
+  const uint2 raw = reinterpret_cast<const uint2*>(x + row * cols + cb * 128)[lane];
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+  const float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]);
+  float amax = fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(b.x), fabsf(b.y)));
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, d));
+  float inv;
+  const uint8_t byte = pow2_scale(amax, inv);
+  const uint32_t packed = to_e4m3(a.x * inv) | (to_e4m3(a.y * inv) << 8) | (to_e4m3(b.x * inv) << 16) |
+                          (to_e4m3(b.y * inv) << 24);
+  reinterpret_cast<uint32_t*>(q + row * cols + cb * 128)[lane] = packed;
+  if (lane == 0) scale[row * ld + cb] = byte;
 }
 
 // One warp per (row, 128-column block): scale = amax / 448 (1 when the block is all zero), q = x / scale.
@@ -120,8 +175,10 @@ __global__ void __launch_bounds__(256) quantize_rows_kernel(const __nv_bfloat16*
 }
 
 // One CTA per 128 x 128 block of a (batch, rows, cols) tensor; rows need not be a multiple of 128.
+// POW2: the scale is a UE8M0 byte (smallest power of two >= amax / 448), else fp32 amax / 448.
+template <bool POW2>
 __global__ void __launch_bounds__(256) quantize_blocks_kernel(const __nv_bfloat16* __restrict__ w,
-                                                              uint8_t* __restrict__ q, float* __restrict__ scale,
+                                                              uint8_t* __restrict__ q, void* __restrict__ scale,
                                                               int rows, int cols) {
   __shared__ float warp_max[8];
   const int cb = blockIdx.x, rb = blockIdx.y, e = blockIdx.z;
@@ -147,6 +204,8 @@ __global__ void __launch_bounds__(256) quantize_blocks_kernel(const __nv_bfloat1
 #pragma unroll
   for (int i = 1; i < 8; ++i) amax = fmaxf(amax, warp_max[i]);
   const float s = amax > 0.f ? amax / 448.f : 1.f;
+  float inv = 1.f;
+  const uint8_t byte = POW2 ? pow2_scale(amax, inv) : 0;
   // pass 2: the block is still in L1/L2
   for (int rr = 0; rr < 16; ++rr) {
     const int r = warp * 16 + rr;
@@ -154,13 +213,19 @@ __global__ void __launch_bounds__(256) quantize_blocks_kernel(const __nv_bfloat1
       const uint2 v = reinterpret_cast<const uint2*>(w + base + static_cast<long long>(r) * cols)[lane];
       const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
       const float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]);
-      const uint32_t packed = to_e4m3(a.x / s) | (to_e4m3(a.y / s) << 8) | (to_e4m3(b.x / s) << 16) |
-                              (to_e4m3(b.y / s) << 24);
+      uint32_t packed;
+      if (POW2)
+        packed = to_e4m3(a.x * inv) | (to_e4m3(a.y * inv) << 8) | (to_e4m3(b.x * inv) << 16) | (to_e4m3(b.y * inv) << 24);
+      else
+        packed = to_e4m3(a.x / s) | (to_e4m3(a.y / s) << 8) | (to_e4m3(b.x / s) << 16) | (to_e4m3(b.y / s) << 24);
       reinterpret_cast<uint32_t*>(q + base + static_cast<long long>(r) * cols)[lane] = packed;
     }
   }
-  if (threadIdx.x == 0)
-    scale[(static_cast<long long>(e) * gridDim.y + rb) * gridDim.x + cb] = s;
+  if (threadIdx.x == 0) {
+    const long long idx = (static_cast<long long>(e) * gridDim.y + rb) * gridDim.x + cb;
+    if (POW2) static_cast<uint8_t*>(scale)[idx] = byte;
+    else static_cast<float*>(scale)[idx] = s;
+  }
 }
 
 }  // namespace fp8
@@ -189,7 +254,7 @@ int smoe_fp8_quantize_rows(const void* x, void* q, float* scale, long long rows,
 int smoe_fp8_quantize_blocks(const void* w, void* q, float* scale, int batch, int rows, int cols, void* stream) {
   if (batch <= 0 || rows <= 0 || cols <= 0 || (cols % 128) != 0) return SMOE_ERR_SHAPE;
   const dim3 grid(cols / 128, (rows + 127) / 128, batch);
-  quantize_blocks_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  quantize_blocks_kernel<false><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(w), static_cast<uint8_t*>(q), scale, rows, cols);
   return cudaGetLastError() == cudaSuccess ? SMOE_OK : SMOE_ERR_LAUNCH;
 }
@@ -269,6 +334,116 @@ int smoe_fp8_up_projection_backward_dx(const void* dzq, const float* dz_scale, c
   // blocks of W1[e] are (j/128, h/128): k-block stride = H/128, n-block stride = 1
   Scales sc = {dz_scale, 2 * I / 128, w1_scale, (long long)(2 * I / 128) * (H / 128), 1, H / 128};
   return launch<false, true, EPI_STORE>(tmA, tmB, p, sc, static_cast<cudaStream_t>(stream));
+}
+
+/* ---- power-of-two (UE8M0) block scales, applied by the tensor cores ---------------------------------- */
+
+int smoe_mxfp8_scale_row_bytes(int cols) { return cols <= 0 ? 0 : 4 * ((cols / 128 + 3) / 4); }
+
+int smoe_mxfp8_quantize_rows(const void* x, void* q, void* scale, long long rows, int cols, void* stream) {
+  if (rows < 0 || cols <= 0 || (cols % 128) != 0) return SMOE_ERR_SHAPE;
+  if (rows == 0) return SMOE_OK;
+  if ((reinterpret_cast<uintptr_t>(scale) & 3u) != 0) return SMOE_ERR_ALIGNMENT;
+  const int ld = smoe_mxfp8_scale_row_bytes(cols);
+  const long long warps = rows * ld;
+  quantize_rows_pow2_kernel<<<static_cast<unsigned>((warps + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), static_cast<uint8_t*>(q), static_cast<uint8_t*>(scale), rows, cols, ld);
+  return cudaGetLastError() == cudaSuccess ? SMOE_OK : SMOE_ERR_LAUNCH;
+}
+
+int smoe_mxfp8_quantize_blocks(const void* w, void* q, void* scale, int batch, int rows, int cols, void* stream) {
+  if (batch <= 0 || rows <= 0 || cols <= 0 || (cols % 128) != 0) return SMOE_ERR_SHAPE;
+  const dim3 grid(cols / 128, (rows + 127) / 128, batch);
+  quantize_blocks_kernel<true><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(w), static_cast<uint8_t*>(q), scale, rows, cols);
+  return cudaGetLastError() == cudaSuccess ? SMOE_OK : SMOE_ERR_LAUNCH;
+}
+
+static mx8::ScaleBytes mx_scales(const void* a, int a_cols, const void* b, long long b_expert, long long b_n,
+                                 long long b_k) {
+  mx8::ScaleBytes sc;
+  sc.a = static_cast<const uint32_t*>(a);
+  sc.a_ld = smoe_mxfp8_scale_row_bytes(a_cols) / 4;
+  sc.b = static_cast<const uint8_t*>(b);
+  sc.b_expert_stride = b_expert;
+  sc.b_n_stride = b_n;
+  sc.b_k_stride = b_k;
+  return sc;
+}
+
+int smoe_mxfp8_up_projection_forward(const void* xq, const void* x_scale, const void* w1q, const void* w1_scale,
+                                     void* z, void* y1, const int* expert_offset, const int* x_gather_idx, int T,
+                                     int H, int I, int E, int TK, int* status, void* stream) {
+  if (bad_shape(H, I, E) || T <= 0 || TK < 0) return SMOE_ERR_SHAPE;
+  if (TK == 0) return SMOE_OK;
+  CUtensorMap tmA, tmB;
+  SMOE_TRY(encode_u8(&tmA, xq, T, H, 1, BK));
+  SMOE_TRY(encode_u8(&tmB, w1q, (uint64_t)E * 2 * I, H, BN_CTA, BK));
+  GemmParams p = {};
+  p.E = E; p.N = 2 * I; p.K = H; p.total_rows = TK; p.gather_rows = T; p.b_rows_per_expert = 2 * I;
+  p.off = expert_offset; p.gather = x_gather_idx;
+  p.out0 = static_cast<__nv_bfloat16*>(z); p.ld0 = 2 * I;
+  p.out1 = static_cast<__nv_bfloat16*>(y1); p.ld1 = I;
+  p.status = status;
+  const mx8::ScaleBytes sc = mx_scales(x_scale, H, w1_scale, (long long)(2 * I / 128) * (H / 128), H / 128, 1);
+  return launch_mx<true, false, EPI_SWIGLU>(tmA, tmB, p, sc, static_cast<cudaStream_t>(stream));
+}
+
+int smoe_mxfp8_down_projection_forward(const void* y1q, const void* y1_scale, const void* w2q, const void* w2_scale,
+                                       void* y2, const int* expert_offset, int H, int I, int E, int TK, int* status,
+                                       void* stream) {
+  if (bad_shape(H, I, E) || TK < 0) return SMOE_ERR_SHAPE;
+  if (TK == 0) return SMOE_OK;
+  CUtensorMap tmA, tmB;
+  SMOE_TRY(encode_u8(&tmA, y1q, TK, I, BM, BK));
+  SMOE_TRY(encode_u8(&tmB, w2q, (uint64_t)E * H, I, BN_CTA, BK));
+  GemmParams p = {};
+  p.E = E; p.N = H; p.K = I; p.total_rows = TK; p.b_rows_per_expert = H;
+  p.off = expert_offset;
+  p.out0 = static_cast<__nv_bfloat16*>(y2); p.ld0 = H;
+  p.status = status;
+  const mx8::ScaleBytes sc = mx_scales(y1_scale, I, w2_scale, (long long)(H / 128) * (I / 128), I / 128, 1);
+  return launch_mx<false, false, EPI_STORE>(tmA, tmB, p, sc, static_cast<cudaStream_t>(stream));
+}
+
+int smoe_mxfp8_down_projection_backward_act(const void* doutq, const void* dout_scale, const void* w2q,
+                                            const void* w2_scale, const void* z, const void* scores,
+                                            int scores_are_bf16, void* dz, void* y1s, float* ds_partial,
+                                            const int* expert_offset, const int* x_gather_idx,
+                                            const int* s_scatter_idx, int T, int H, int I, int E, int TK, int* status,
+                                            void* stream) {
+  if (bad_shape(H, I, E) || TK < 0 || T <= 0) return SMOE_ERR_SHAPE;
+  if (TK == 0) return SMOE_OK;
+  CUtensorMap tmA, tmB;
+  SMOE_TRY(encode_u8(&tmA, doutq, T, H, 1, BK));
+  SMOE_TRY(encode_u8(&tmB, w2q, (uint64_t)E * H, I, BK, BN_CTA));  // W2[e] (H, I): rows are k
+  GemmParams p = {};
+  p.E = E; p.N = I; p.K = H; p.total_rows = TK; p.gather_rows = T; p.b_rows_per_expert = H;
+  p.off = expert_offset; p.gather = x_gather_idx; p.s_scatter = s_scatter_idx;
+  p.out0 = static_cast<__nv_bfloat16*>(dz); p.ld0 = 2 * I;
+  p.out1 = static_cast<__nv_bfloat16*>(y1s); p.ld1 = I;
+  p.z = static_cast<const __nv_bfloat16*>(z);
+  p.scores = scores; p.scores_are_bf16 = scores_are_bf16; p.ds_partial = ds_partial;
+  p.status = status;
+  const mx8::ScaleBytes sc = mx_scales(dout_scale, H, w2_scale, (long long)(H / 128) * (I / 128), 1, I / 128);
+  return launch_mx<true, true, EPI_DSWIGLU>(tmA, tmB, p, sc, static_cast<cudaStream_t>(stream));
+}
+
+int smoe_mxfp8_up_projection_backward_dx(const void* dzq, const void* dz_scale, const void* w1q, const void* w1_scale,
+                                         void* dx_expanded, const int* expert_offset, int H, int I, int E, int TK,
+                                         int* status, void* stream) {
+  if (bad_shape(H, I, E) || TK < 0) return SMOE_ERR_SHAPE;
+  if (TK == 0) return SMOE_OK;
+  CUtensorMap tmA, tmB;
+  SMOE_TRY(encode_u8(&tmA, dzq, TK, 2 * I, BM, BK));
+  SMOE_TRY(encode_u8(&tmB, w1q, (uint64_t)E * 2 * I, H, BK, BN_CTA));  // W1[e] (2I, H): rows are k
+  GemmParams p = {};
+  p.E = E; p.N = H; p.K = 2 * I; p.total_rows = TK; p.b_rows_per_expert = 2 * I;
+  p.off = expert_offset;
+  p.out0 = static_cast<__nv_bfloat16*>(dx_expanded); p.ld0 = H;
+  p.status = status;
+  const mx8::ScaleBytes sc = mx_scales(dz_scale, 2 * I, w1_scale, (long long)(2 * I / 128) * (H / 128), 1, H / 128);
+  return launch_mx<false, true, EPI_STORE>(tmA, tmB, p, sc, static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

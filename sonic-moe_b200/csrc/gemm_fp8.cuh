@@ -55,7 +55,8 @@ struct Tile {
   int e, row0, row_end, n0, num_kb;
 };
 
-__device__ __forceinline__ bool decode_tile(const GemmParams& p, const SharedStorage& ss, long long t, int num_n,
+template <class Storage>
+__device__ __forceinline__ bool decode_tile(const GemmParams& p, const Storage& ss, long long t, int num_n,
                                             uint32_t rank, Tile& tile) {
   const int total_m = ss.m_tile_prefix[p.E];
   if (t >= static_cast<long long>(total_m) * num_n) return false;

@@ -1,6 +1,7 @@
-"""FP8 (E4M3, 1x128 / 128x128 fp32 block scales) path: quantisation kernels, each FP8 GEMM against the exact
-dequantised fp32 product, and the whole layer against the fp32 oracle on the bf16 master weights
-(relative Frobenius error <= 3e-2, the bound stated for the FP8 layer)."""
+"""FP8 (E4M3, 1x128 / 128x128 block scales) path in both scale formats -- fp32 amax/448 scales applied in software
+and power-of-two UE8M0 scales applied by the tensor cores: quantisation kernels, each FP8 GEMM against the exact
+dequantised fp32 product, and the whole layer against a CPU simulation and the fp32 oracle on the bf16 master
+weights."""
 
 import pytest
 import torch
@@ -58,11 +59,48 @@ def test_quantize_blocks(built_library, E, rows, cols):
     assert rel(dequant_blocks(q, s), w) < 0.04
 
 
-SHAPES = [(512, 256, 128, 4, 2, False), (1000, 512, 256, 8, 2, True), (300, 128, 128, 16, 4, True)]
+@pytest.mark.parametrize("rows,cols", [(1, 128), (1000, 256), (4096, 1024), (333, 640)])
+def test_quantize_rows_pow2(built_library, rows, cols):
+    from oracle import fp8_sim
+    from sonicmoe.functional import fp8
+
+    g = torch.Generator().manual_seed(rows)
+    x = (torch.randn(rows, cols, generator=g) * torch.rand(rows, 1, generator=g) * 3).bfloat16()
+    x[0, :128] = 0                      # an all-zero block keeps scale 2^0
+    if rows > 2:
+        x[1, :128] = 0
+        x[1, 5] = 448.0                 # amax / 448 exactly a power of two
+        x[2, :128] = 2.0 ** -130        # scale clamps at 2^-127
+    q, s = fp8.quantize_rows(x.cuda(), "ue8m0")
+    nblk = cols // 128
+    assert s.dtype == torch.uint8 and s.shape == (rows, 4 * ((nblk + 3) // 4))
+    amax = x.float().view(rows, nblk, 128).abs().amax(-1)
+    want = fp8_sim.block_scale(amax, pow2=True)
+    assert torch.equal(torch.exp2(s.cpu()[:, :nblk].float() - 127.0), want)
+    assert (s.cpu()[:, nblk:] == 127).all()
+    # bit-exact with the simulation's quantise-dequantise
+    assert torch.equal(fp8.dequantize(q, s).cpu(), fp8_sim.quant_rows(x.float(), pow2=True))
 
 
+@pytest.mark.parametrize("E,rows,cols", [(2, 128, 128), (3, 320, 256), (4, 512, 1024)])
+def test_quantize_blocks_pow2(built_library, E, rows, cols):
+    from oracle import fp8_sim
+    from sonicmoe.functional import fp8
+
+    g = torch.Generator().manual_seed(rows + E)
+    w = (torch.randn(E, rows, cols, generator=g) * 0.02).bfloat16()
+    q, s = fp8.quantize_blocks(w.cuda(), "ue8m0")
+    assert s.dtype == torch.uint8 and s.shape == (E, (rows + 127) // 128, cols // 128)
+    assert torch.equal(fp8.dequantize(q, s).cpu(), fp8_sim.quant_blocks(w.float(), pow2=True))
+
+
+SHAPES = [(512, 256, 128, 4, 2, False), (1000, 512, 256, 8, 2, True), (300, 128, 128, 16, 4, True),
+          (2048, 1024, 640, 8, 4, False)]   # the last: 8 and 5 k-blocks (two scale words per row, a partial group)
+
+
+@pytest.mark.parametrize("fmt", ["fp32", "ue8m0"])
 @pytest.mark.parametrize("shape", SHAPES)
-def test_fp8_gemms_match_dequantised_products(built_library, shape):
+def test_fp8_gemms_match_dequantised_products(built_library, shape, fmt):
     """Each FP8 GEMM computes exactly sum_kb (A_q . B_q)_kb * sa * sb in fp32: compare with that product."""
     from sonicmoe import _lib
     from sonicmoe.functional import fp8
@@ -86,16 +124,16 @@ def test_fp8_gemms_match_dequantised_products(built_library, shape):
     d_off, d_gat, d_sct = (route.expert_frequency_offset.cuda(), route.x_gather_idx.cuda(), route.s_scatter_idx.cuda())
 
     x, w1, w2, dout = inp["x"].cuda(), inp["w1"].cuda(), inp["w2"].cuda(), inp["dout"].cuda()
-    xq, xs = fp8.quantize_rows(x)
-    w1q, w1s = fp8.quantize_blocks(w1)
-    w2q, w2s = fp8.quantize_blocks(w2)
-    xd, w1d, w2d = dequant_rows(xq, xs).cpu(), dequant_blocks(w1q, w1s).cpu(), dequant_blocks(w2q, w2s).cpu()
+    xq, xs = fp8.quantize_rows(x, fmt)
+    w1q, w1s = fp8.quantize_blocks(w1, fmt)
+    w2q, w2s = fp8.quantize_blocks(w2, fmt)
+    xd, w1d, w2d = fp8.dequantize(xq, xs).cpu(), fp8.dequantize(w1q, w1s).cpu(), fp8.dequantize(w2q, w2s).cpu()
 
     # up projection
     nan = float("nan")
     z = torch.full((TK, 2 * I), nan, dtype=torch.bfloat16, device=dev)
     y1 = torch.full((TK, I), nan, dtype=torch.bfloat16, device=dev)
-    assert lib.smoe_fp8_up_projection_forward(xq.data_ptr(), xs.data_ptr(), w1q.data_ptr(), w1s.data_ptr(),
+    assert fp8._entry("up_projection_forward", fmt)(xq.data_ptr(), xs.data_ptr(), w1q.data_ptr(), w1s.data_ptr(),
                                               z.data_ptr(), y1.data_ptr(), d_off.data_ptr(), d_gat.data_ptr(),
                                               T, H, I, E, TK, st.data_ptr(), stream) == 0
     z_ref = torch.empty(TK, 2 * I)
@@ -105,10 +143,10 @@ def test_fp8_gemms_match_dequantised_products(built_library, shape):
 
     # down projection
     y1b = orc.swiglu(z_ref).bfloat16().cuda()
-    y1q, y1s = fp8.quantize_rows(y1b)
-    y1d = dequant_rows(y1q, y1s).cpu()
+    y1q, y1s = fp8.quantize_rows(y1b, fmt)
+    y1d = fp8.dequantize(y1q, y1s).cpu()
     y2 = torch.full((TK, H), nan, dtype=torch.bfloat16, device=dev)
-    assert lib.smoe_fp8_down_projection_forward(y1q.data_ptr(), y1s.data_ptr(), w2q.data_ptr(), w2s.data_ptr(),
+    assert fp8._entry("down_projection_forward", fmt)(y1q.data_ptr(), y1s.data_ptr(), w2q.data_ptr(), w2s.data_ptr(),
                                                 y2.data_ptr(), d_off.data_ptr(), H, I, E, TK, st.data_ptr(),
                                                 stream) == 0
     y2_ref = torch.empty(TK, H)
@@ -117,8 +155,8 @@ def test_fp8_gemms_match_dequantised_products(built_library, shape):
     assert rel(y2, y2_ref) < 1e-2
 
     # dH with the dSwiGLU epilogue
-    dq, dsc = fp8.quantize_rows(dout)
-    dd = dequant_rows(dq, dsc).cpu()
+    dq, dsc = fp8.quantize_rows(dout, fmt)
+    dd = fp8.dequantize(dq, dsc).cpu()
     zb = z_ref.bfloat16()
     dz = torch.full((TK, 2 * I), nan, dtype=torch.bfloat16, device=dev)
     ys = torch.full((TK, I), nan, dtype=torch.bfloat16, device=dev)
@@ -126,7 +164,7 @@ def test_fp8_gemms_match_dequantised_products(built_library, shape):
     dsp = torch.zeros(ncols, TK, dtype=torch.float32, device=dev)
     sc = scores.reshape(-1).cuda()
     zdev = zb.cuda()
-    assert lib.smoe_fp8_down_projection_backward_act(
+    assert fp8._entry("down_projection_backward_act", fmt)(
         dq.data_ptr(), dsc.data_ptr(), w2q.data_ptr(), w2s.data_ptr(), zdev.data_ptr(), sc.data_ptr(), 0,
         dz.data_ptr(), ys.data_ptr(), dsp.data_ptr(), d_off.data_ptr(), d_gat.data_ptr(), d_sct.data_ptr(),
         T, H, I, E, TK, st.data_ptr(), stream) == 0
@@ -144,10 +182,10 @@ def test_fp8_gemms_match_dequantised_products(built_library, shape):
 
     # dX
     dzb = dz_ref.bfloat16().cuda()
-    dzq, dzs = fp8.quantize_rows(dzb)
-    dzd = dequant_rows(dzq, dzs).cpu()
+    dzq, dzs = fp8.quantize_rows(dzb, fmt)
+    dzd = fp8.dequantize(dzq, dzs).cpu()
     dxe = torch.full((TK, H), nan, dtype=torch.bfloat16, device=dev)
-    assert lib.smoe_fp8_up_projection_backward_dx(dzq.data_ptr(), dzs.data_ptr(), w1q.data_ptr(), w1s.data_ptr(),
+    assert fp8._entry("up_projection_backward_dx", fmt)(dzq.data_ptr(), dzs.data_ptr(), w1q.data_ptr(), w1s.data_ptr(),
                                                   dxe.data_ptr(), d_off.data_ptr(), H, I, E, TK, st.data_ptr(),
                                                   stream) == 0
     dx_ref = torch.empty(TK, H)
@@ -158,8 +196,9 @@ def test_fp8_gemms_match_dequantised_products(built_library, shape):
     assert st.item() == 0
 
 
+@pytest.mark.parametrize("fmt", ["fp32", "ue8m0"])
 @pytest.mark.parametrize("T,H,I,E,K", [(512, 256, 128, 16, 4), (1024, 512, 256, 8, 2), (777, 1024, 384, 32, 8)])
-def test_fp8_layer(built_library, T, H, I, E, K):
+def test_fp8_layer(built_library, T, H, I, E, K, fmt):
     """Whole FP8 layer.
 
     Kernel numerics: against a CPU simulation with the same quantisation points (oracle/fp8_sim.py), <= 2e-2
@@ -182,7 +221,8 @@ def test_fp8_layer(built_library, T, H, I, E, K):
     rw = inp["router_w"].cuda().requires_grad_(True)
     w1 = inp["w1"].cuda().requires_grad_(True)
     w2 = inp["w2"].cuda().requires_grad_(True)
-    o, logits, freq = moe_fp8_softmax_topk_layer(x, rw, w1.permute(1, 2, 0), None, w2.permute(1, 2, 0), None, K)
+    o, logits, freq = moe_fp8_softmax_topk_layer(x, rw, w1.permute(1, 2, 0), None, w2.permute(1, 2, 0), None, K,
+                                                 scale_format=fmt)
     scores_dev, idx = topk_softmax(logits.detach(), K)
     # gradient of the expert path only (scores detached) so that it can be compared term by term
     grads = torch.autograd.grad(o, [x, w1, w2], inp["dout"].cuda())
@@ -193,7 +233,8 @@ def test_fp8_layer(built_library, T, H, I, E, K):
                         logits=logits.detach().float().cpu())
     assert torch.equal(idx.cpu(), ref["indices"])
     assert torch.equal(freq.cpu(), ref["expert_frequency"])
-    sim = fp8_sim.experts_forward_backward(f32["x"], f32["w1"], f32["w2"], ref["scores"], ref["route"], f32["dout"])
+    sim = fp8_sim.experts_forward_backward(f32["x"], f32["w1"], f32["w2"], ref["scores"], ref["route"], f32["dout"],
+                                           pow2=fmt == "ue8m0")
     dlogits = orc.softmax_topk_backward(ref["scores"], ref["indices"], sim["ds"].reshape(T, K), E)
     sim_dx = sim["dx"] + dlogits @ f32["router_w"]
     ref_pairs = {"o": (o, sim["o"], ref["o"]), "dx": (grads[0], sim_dx, ref["dx"]),
