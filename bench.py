@@ -484,7 +484,7 @@ def run_ep_arm(args, rank, world, local_rank, fp8=False):
     from sonicmoe.expert_parallel import Fp8CudaOps, moe_ep_softmax_topk_layer
 
     cfg = EP_FP8_CFG if fp8 else EP_CFG
-    ops = Fp8CudaOps() if fp8 else None
+    ops = Fp8CudaOps(args.fp8_scales) if fp8 else None
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
     dist.init_process_group("nccl", device_id=dev)
@@ -543,6 +543,7 @@ def run_ep_arm(args, rank, world, local_rank, fp8=False):
                                     "moe_layer_fwd_bwd_expert_parallel_zipf_T65536_per_gpu_H2048_I768_E64_K4"), **cfg,
                        "parallelism": f"ep{world}",
                        "routing": "softmax_topk" if fp8 else "softmax_topk + per-expert logit bias 2*log(1/rank)"},
+            **({"fp8_scale_format": args.fp8_scales} if fp8 else {}),
             "expert_load_max_over_mean": (freq.max() / freq.mean()).item(),
             "rank_load_max_over_mean": (per_rank_rows.max() / per_rank_rows.mean()).item(),
         }
@@ -563,6 +564,8 @@ def main():
     ap.add_argument("--experts", type=int, default=CFG["E"])
     ap.add_argument("--reps", type=int, default=5)
     ap.add_argument("--workload", default="topk", choices=["topk", "ep_zipf", "ep_fp8", "token_rounding"])
+    # ep_fp8: "fp32" = amax/448 scales applied in software, "ue8m0" = rounded up to a power of two, applied by the tensor cores
+    ap.add_argument("--fp8-scales", default="ue8m0", choices=["fp32", "ue8m0"])
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -81,7 +81,11 @@ class CudaOps:
 
 
 class Fp8CudaOps(CudaOps):
-    """As CudaOps, with the local experts' forward and activation-gradient GEMMs in FP8 (E4M3, block scales)."""
+    """As CudaOps, with the local experts' forward and activation-gradient GEMMs in FP8 (E4M3, block scales;
+    ``scale_format`` "fp32", "ue8m0" or None for the FP8 module's default)."""
+
+    def __init__(self, scale_format: str | None = None):
+        self.scale_format = scale_format
 
     def local_experts(self, x_rows, w1, w2, scores, local_expert, num_local_experts, inference):
         from . import functional as fn
@@ -91,7 +95,8 @@ class Fp8CudaOps(CudaOps):
         rows = torch.arange(R, dtype=torch.int32, device=x_rows.device)
         route = fn._route_metadata(local_expert, rows, num_local_experts, 0)
         route.K = 1
-        return _RoutedExpertsFp8.apply(x_rows, w1.permute(1, 2, 0), w2.permute(1, 2, 0), scores, route, R, inference)
+        return _RoutedExpertsFp8.apply(x_rows, w1.permute(1, 2, 0), w2.permute(1, 2, 0), scores, route, R, inference,
+                                       self.scale_format)
 
 
 class _GatherRows(torch.autograd.Function):
