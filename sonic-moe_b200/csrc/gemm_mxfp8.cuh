@@ -17,7 +17,7 @@
 //            memory back to the MMA issuer at once, then run the fused epilogue from registers
 //   warps 12..15 row gather with TMA tile::gather4
 //
-// Tensor memory: columns 0..255 accumulator, 256.. two sets of scale factors (4 columns A + 8 columns B each).
+// Tensor memory: columns 0..255 accumulator, 256.. four sets of scale factors (4 columns A + 8 columns B each).
 // Ragged-M only; every wait is bounded.
 #pragma once
 #include "gemm_fp8.cuh"
@@ -44,7 +44,7 @@ constexpr int KB_PER_GROUP = 4;          // k-blocks whose scale bytes share one
 constexpr int SFA_BYTES = 512;           // 128 rows x 4 bytes
 constexpr int SFB_BYTES = 1024;          // 256 columns x 4 bytes
 constexpr int SF_SET_BYTES = SFA_BYTES + SFB_BYTES;
-constexpr int SF_SETS = 2;
+constexpr int SF_SETS = 4;             // groups the scale-factor warps may run ahead of the MMA issuer
 constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t TMEM_SF_COL = 256;    // first scale-factor column
 constexpr uint32_t TMEM_SF_SET_COLS = 32;
@@ -276,8 +276,8 @@ grouped_gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
             b_src[h] = sc.b + tile.e * sc.b_expert_stride +
                        static_cast<long long>(min(tile.n0 / 128 + h, nblocks - 1)) * sc.b_n_stride;
         }
-        for (int g = 0; g < groups; ++g) {
-          uint4 w0, w1 = make_uint4(0, 0, 0, 0);
+        // words of group g: A rows (warp 2) or the tile's two weight blocks (warp 3); loaded one group ahead
+        auto load_words = [&](int g, uint4& w0, uint4& w1) {
           if (warp == 2) {
             // 0x7F = 2^0: rows past the expert's end are computed and never stored
             w0.x = a_src[0] ? a_src[0][g] : 0x7F7F7F7Fu;
@@ -299,6 +299,12 @@ grouped_gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
             w0 = make_uint4(w[0], w[0], w[0], w[0]);
             w1 = make_uint4(w[1], w[1], w[1], w[1]);
           }
+        };
+        uint4 w0, w1 = make_uint4(0, 0, 0, 0);
+        load_words(0, w0, w1);
+        for (int g = 0; g < groups; ++g) {
+          uint4 n0 = w0, n1 = w1;
+          if (g + 1 < groups) load_words(g + 1, n0, n1);
           if (!mbar_wait(smem_u32(&ss.sf_empty[set]), set_phase ^ 1u, abort_flag)) { ok = false; break; }
           uint8_t* dst = sSF + set * SF_SET_BYTES;
           if (warp == 2) {
@@ -307,10 +313,14 @@ grouped_gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
             reinterpret_cast<uint4*>(dst + SFA_BYTES)[lane] = w0;        // columns 0..127 of the tile
             reinterpret_cast<uint4*>(dst + SFA_BYTES + 512)[lane] = w1;  // columns 128..255
           }
+          // the words are in shared memory (and visible to the tensor cores' proxy) long before the arrive,
+          // which crosses to the leader CTA, lets the MMA warp issue the copy
           fence_proxy_async_smem();
           __syncwarp();
-          if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&ss.sf_full[set]), 0));
+          if (lane == 0) mbar_arrive_cluster_relaxed(map_to_cta(smem_u32(&ss.sf_full[set]), 0));
           if (++set == SF_SETS) { set = 0; set_phase ^= 1u; }
+          w0 = n0;
+          w1 = n1;
         }
       }
       if (!ok && lane == 0 && p.status) atomicCAS(p.status, ST_OK, ST_TIMEOUT_PRODUCER);
