@@ -552,6 +552,112 @@ def run_ep_arm(args, rank, world, local_rank, fp8=False):
     dist.destroy_process_group()
 
 
+
+def run_fp8_arm(args, local_rank):
+    """The benchmark layer (BASELINE configs[1] shapes) with the expert GEMMs of forward and activation gradients in
+    FP8 E4M3 (1x128 / 128x128 block scales, `--fp8-scales`), weight gradients in bf16: a side workload, not the
+    headline line (whose dtype is bf16).  `--kernels-only` times each FP8 GEMM alone on `--tokens` / `--experts`
+    (the command the ncu captures of these kernels use)."""
+    from sonicmoe import _lib
+    from sonicmoe.functional import _route_metadata, fp8, topk_softmax
+
+    fmt = args.fp8_scales
+    cfg = dict(CFG, T=args.tokens, E=args.experts) if args.kernels_only else dict(CFG)
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    T, H, I, E, K = (cfg[k] for k in "THIEK")
+    TK = T * K
+    g = torch.Generator(device=dev).manual_seed(0)
+    router_w = (torch.randn(E, H, generator=g, device=dev) * 0.02).bfloat16().requires_grad_(True)
+    w1 = (torch.randn(E, 2 * I, H, generator=g, device=dev) * 0.02).bfloat16().requires_grad_(True)
+    w2 = (torch.randn(E, H, I, generator=g, device=dev) * 0.02).bfloat16().requires_grad_(True)
+    x = torch.randn(T, H, generator=g, device=dev).bfloat16().requires_grad_(True)
+    dout = torch.randn(T, H, generator=g, device=dev).bfloat16()
+
+    def timed(fn, n):
+        fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / n
+
+    if args.kernels_only:
+        lib = _lib.lib
+        with torch.no_grad():
+            scores, idx = topk_softmax(torch.randn(T, E, generator=g, device=dev), K)
+            route = _route_metadata(idx.reshape(-1), None, E, K)
+            off, gat, sct = (route.expert_frequency_offset.data_ptr(), route.x_gather_idx.data_ptr(),
+                             route.s_scatter_idx.data_ptr())
+            st = _lib.device_state(dev).status.data_ptr()
+            stream = torch.cuda.current_stream().cuda_stream
+            xq, xs = fp8.quantize_rows(x.detach(), fmt)
+            w1q, w1s = fp8.quantize_blocks(w1.detach(), fmt)
+            w2q, w2s = fp8.quantize_blocks(w2.detach(), fmt)
+            z = torch.randn(TK, 2 * I, device=dev).bfloat16()
+            y1 = torch.randn(TK, I, device=dev).bfloat16()
+            y2 = torch.empty(TK, H, dtype=torch.bfloat16, device=dev)
+            dz = torch.empty_like(z)
+            y1s = torch.empty_like(y1)
+            y1q, y1sc = fp8.quantize_rows(y1, fmt)
+            zq, zs = fp8.quantize_rows(z, fmt)
+            dq, dqs = fp8.quantize_rows(dout, fmt)
+            dsp = torch.empty(lib.smoe_ds_partial_columns(I), TK, dtype=torch.float32, device=dev)
+            sc = scores.reshape(-1).contiguous()
+            unit = 2.0 * TK * I * H
+            calls = {
+                "quantize_rows(x)": (0.0, lambda: fp8.quantize_rows(x.detach(), fmt)),
+                "quantize_blocks(w1)": (0.0, lambda: fp8.quantize_blocks(w1.detach(), fmt)),
+                "up_projection_forward": (2 * unit, lambda: fp8._entry("up_projection_forward", fmt)(
+                    xq.data_ptr(), xs.data_ptr(), w1q.data_ptr(), w1s.data_ptr(), z.data_ptr(), y1.data_ptr(), off, gat,
+                    T, H, I, E, TK, st, stream)),
+                "down_projection_forward": (unit, lambda: fp8._entry("down_projection_forward", fmt)(
+                    y1q.data_ptr(), y1sc.data_ptr(), w2q.data_ptr(), w2s.data_ptr(), y2.data_ptr(), off, H, I, E, TK, st,
+                    stream)),
+                "down_projection_backward_act": (unit, lambda: fp8._entry("down_projection_backward_act", fmt)(
+                    dq.data_ptr(), dqs.data_ptr(), w2q.data_ptr(), w2s.data_ptr(), z.data_ptr(), sc.data_ptr(), 0,
+                    dz.data_ptr(), y1s.data_ptr(), dsp.data_ptr(), off, gat, sct, T, H, I, E, TK, st, stream)),
+                "up_projection_backward_dx": (2 * unit, lambda: fp8._entry("up_projection_backward_dx", fmt)(
+                    zq.data_ptr(), zs.data_ptr(), w1q.data_ptr(), w1s.data_ptr(), y2.data_ptr(), off, H, I, E, TK, st,
+                    stream)),
+            }
+            kernels = {}
+            for name, (flops, fn) in calls.items():
+                ms = timed(fn, args.reps)
+                kernels[name] = {"ms": ms, **({"tflops": flops / ms / 1e9} if flops else {})}
+        _lib.check_status(dev)
+        print(json.dumps({"config": {**cfg, "fp8_scale_format": fmt}, "kernels": kernels}), flush=True)
+        return
+
+    params = [x, router_w, w1, w2]
+
+    def step():
+        for p_ in params:
+            p_.grad = None
+        o, _logits, _freq = fp8.moe_fp8_softmax_topk_layer(x, router_w, w1.permute(1, 2, 0), None, w2.permute(1, 2, 0),
+                                                           None, K, scale_format=fmt)
+        o.backward(dout)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    ms = timed(step, args.steps)
+    clocks = sampler.stop()
+    _lib.check_status(dev)
+    value = 18.0 * TK * I * H / (ms * 1e-3) / 1e12
+    print(json.dumps({
+        "metric": "moe_fwd_bwd_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "fp8_e4m3 (weight gradients bf16)", "data": "synthetic",
+        "tokens_per_s": T / (ms * 1e-3), "fp8_scale_format": fmt, "clocks": clocks,
+        "config": {"workload": "moe_layer_fwd_bwd_fp8_T32768_H4096_I1024_E128_K8", **cfg},
+    }), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -563,7 +669,7 @@ def main():
     ap.add_argument("--tokens", type=int, default=CFG["T"])
     ap.add_argument("--experts", type=int, default=CFG["E"])
     ap.add_argument("--reps", type=int, default=5)
-    ap.add_argument("--workload", default="topk", choices=["topk", "ep_zipf", "ep_fp8", "token_rounding"])
+    ap.add_argument("--workload", default="topk", choices=["topk", "ep_zipf", "ep_fp8", "token_rounding", "fp8"])
     # ep_fp8: "fp32" = amax/448 scales applied in software, "ue8m0" = rounded up to a power of two, applied by the tensor cores
     ap.add_argument("--fp8-scales", default="ue8m0", choices=["fp32", "ue8m0"])
     args = ap.parse_args()
@@ -577,6 +683,9 @@ def main():
         raise SystemExit("bench.py needs a CUDA device: the layer has no CPU path (use --impl reference for the CPU arm)")
     if args.workload == "token_rounding":
         run_rounding_arm(args, local_rank)
+        return
+    if args.workload == "fp8":
+        run_fp8_arm(args, local_rank)
         return
     if args.workload in ("ep_zipf", "ep_fp8"):
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
