@@ -108,21 +108,35 @@ static bool use_cta_pair() {
   return v;
 }
 
-template <bool RAGGED_K, bool A_GATHER, bool A_MN, bool B_GATHER, bool B_MN, int EPI, int EW, int GW, bool TG = false>
+// Kernels with a gathered operand work on two tiles per gathered stage (256 x 512 or 512 x 256 units) unless
+// SMOE_DUAL=0.
+static bool use_dual_tiles() {
+  static const bool v = env_int("SMOE_DUAL", 1) != 0;
+  return v;
+}
+
+template <bool RAGGED_K, bool A_GATHER, bool A_MN, bool B_GATHER, bool B_MN, int EPI, int EW, int GW, bool TG = false,
+          int DUAL = pair::DUAL_NONE>
 static int launch_pair_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p,
                                cudaStream_t stream) {
-  auto kernel = pair::grouped_gemm_pair_kernel<RAGGED_K, A_GATHER, A_MN, B_GATHER, B_MN, EPI, EW, GW, TG>;
+  auto kernel = pair::grouped_gemm_pair_kernel<RAGGED_K, A_GATHER, A_MN, B_GATHER, B_MN, EPI, EW, GW, TG, DUAL>;
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, pair::SMEM_BYTES) != cudaSuccess)
       return SMOE_ERR_LAUNCH;
+    if (DUAL != pair::DUAL_NONE) {
+      // the kernel re-partitions registers between its warpgroups (setmaxnreg 56 / 200 around 128): that only
+      // balances if it was compiled to exactly 128 registers per thread -- refuse to launch otherwise
+      cudaFuncAttributes fa;
+      if (cudaFuncGetAttributes(&fa, kernel) != cudaSuccess || fa.numRegs != 128) return SMOE_ERR_LAUNCH;
+    }
     configured = true;
   }
   const int sms = num_sms();
   if (sms < 2) return SMOE_ERR_DRIVER;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(sms & ~1), 1, 1);
-  cfg.blockDim = dim3(pair::threads(EW, GW), 1, 1);
+  cfg.blockDim = dim3(pair::threads(EW, GW, DUAL != pair::DUAL_NONE), 1, 1);
   cfg.dynamicSmemBytes = pair::SMEM_BYTES;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
@@ -151,6 +165,12 @@ static int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const Gem
     SMOE_LAUNCH(8, 0);
   } else {
     if (use_tma_gather_pair()) {
+      // (not for the activation-gradient epilogues: they are long enough that losing the overlap of epilogue and
+      // main loop costs more than the halved gather traffic gains: 2.3-2.5 ms against 2.2 ms)
+      if (use_dual_tiles() && EPI != EPI_DSWIGLU && EPI != EPI_DACT) {
+        constexpr int kDual = A_GATHER ? pair::DUAL_N : pair::DUAL_M;
+        return launch_pair_variant<RAGGED_K, A_GATHER, A_MN, B_GATHER, B_MN, EPI, 8, 4, true, kDual>(tmA, tmB, p, stream);
+      }
       if (gw == 8) return launch_pair_variant<RAGGED_K, A_GATHER, A_MN, B_GATHER, B_MN, EPI, 4, 8, true>(tmA, tmB, p, stream);
       return launch_pair_variant<RAGGED_K, A_GATHER, A_MN, B_GATHER, B_MN, EPI, 4, 4, true>(tmA, tmB, p, stream);
     }

@@ -68,6 +68,9 @@ static int launch_kernel(Kernel kernel, bool& configured, int smem_bytes, const 
   if (!configured) {
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) != cudaSuccess)
       return SMOE_ERR_LAUNCH;
+    // setmaxnreg 56 / 200 in these kernels balances only around 128 registers per thread at launch
+    cudaFuncAttributes fa;
+    if (cudaFuncGetAttributes(&fa, kernel) != cudaSuccess || fa.numRegs != 128) return SMOE_ERR_LAUNCH;
     configured = true;
   }
   const int sms = num_sms();

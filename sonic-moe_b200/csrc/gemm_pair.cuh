@@ -4,6 +4,12 @@
 // accumulator (this CTA's 128 rows x all 256 columns, fp32) lives in the CTA's own tensor memory, two
 // of them so the epilogue of one tile overlaps the main loop of the next.
 //
+// DUAL mode (kernels with a gathered operand): one work unit is two tiles that share the gathered operand's
+// stage -- 256 x 512 (DUAL_N: two B tiles) or 512 x 256 (DUAL_M: two A tiles) -- one per accumulator.  A stage
+// is then 48 KiB (gathered tile + two plain tiles), four stages deep, and every gathered row feeds twice the
+// MMA work, which is what bounds these kernels (row gathers are many small TMA operations); the price is that
+// the two accumulators no longer alternate between consecutive units.
+//
 // Roles per CTA (warp index):
 //   0        TMA producer for the operands that are not gathered (both CTAs; completion bytes are counted
 //            on the leader CTA's "full" barrier)
@@ -34,7 +40,11 @@ constexpr int B_STAGE_BYTES = BN_CTA * BK * 2;   // 16 KiB
 constexpr int CHUNK_BYTES = BK * 128;            // 64-element MN chunk: BK rows x 128 B
 constexpr int MAX_EXPERTS = 1024;
 
-__host__ __device__ constexpr int threads(int epi_warps, int gather_warps) { return 32 * (2 + epi_warps + gather_warps); }
+// DUAL kernels keep warps 2 and 3 idle so that every role fills whole warpgroups (setmaxnreg is a warpgroup-wide
+// instruction): warps 0-3 producer / MMA, 4-11 epilogue, 12-15 gather.
+__host__ __device__ constexpr int threads(int epi_warps, int gather_warps, bool dual = false) {
+  return 32 * ((dual ? 4 : 2) + epi_warps + gather_warps);
+}
 
 struct SharedStorage {
   uint64_t full[STAGES];
@@ -58,9 +68,14 @@ struct Tile {
   int num_kb;
 };
 
-template <bool RAGGED_K>
+enum { DUAL_NONE = 0, DUAL_N = 1, DUAL_M = 2 };
+
+// num_n counts work units along N (DUAL_N: 512 columns each).
+template <bool RAGGED_K, int DUAL = DUAL_NONE>
 __device__ __forceinline__ bool decode_tile(const GemmParams& p, const SharedStorage& ss, long long t, int num_n,
                                             uint32_t rank, Tile& tile) {
+  constexpr int UNIT_N = DUAL == DUAL_N ? 2 * BN : BN;
+  constexpr int UNIT_M = DUAL == DUAL_M ? 4 * BM : 2 * BM;
   if constexpr (!RAGGED_K) {
     const int total_m = ss.m_tile_prefix[p.E];
     if (t >= static_cast<long long>(total_m) * num_n) return false;
@@ -74,21 +89,21 @@ __device__ __forceinline__ bool decode_tile(const GemmParams& p, const SharedSto
     tile.e = lo;
     tile.row0 = p.off[lo] + (mi - ss.m_tile_prefix[lo]) * (2 * BM) + static_cast<int>(rank) * BM;
     tile.row_end = p.off[lo + 1];
-    tile.n0 = ni * BN;
+    tile.n0 = ni * UNIT_N;
     tile.k_begin = 0;
     tile.k_end = p.K;
     tile.num_kb = p.K / BK;
     return true;
   } else {
-    const int num_m = (p.M + 2 * BM - 1) / (2 * BM);
+    const int num_m = (p.M + UNIT_M - 1) / UNIT_M;
     const long long per_e = static_cast<long long>(num_m) * num_n;
     if (t >= per_e * p.E) return false;
     const int e = static_cast<int>(t / per_e);
     const int rem = static_cast<int>(t % per_e);
     tile.e = e;
-    tile.row0 = (rem / num_n) * (2 * BM) + static_cast<int>(rank) * BM;
+    tile.row0 = (rem / num_n) * UNIT_M + static_cast<int>(rank) * BM;
     tile.row_end = p.M;
-    tile.n0 = (rem % num_n) * BN;
+    tile.n0 = (rem % num_n) * UNIT_N;
     tile.k_begin = p.off[e];
     tile.k_end = p.off[e + 1];
     tile.num_kb = (tile.k_end - tile.k_begin + BK - 1) / BK;
@@ -98,15 +113,22 @@ __device__ __forceinline__ bool decode_tile(const GemmParams& p, const SharedSto
 
 // TG: the gather warps fetch rows with TMA tile::gather4 (32 issuing threads spread over the gather warps)
 // instead of 16-byte cp.async copies; completion then goes straight to the leader's full barrier.
-template <bool RAGGED_K, bool A_GATHER, bool A_MN, bool B_GATHER, bool B_MN, int EPI, int EW, int GW, bool TG = false>
-__global__ void __launch_bounds__(threads(EW, GW), 1)
+template <bool RAGGED_K, bool A_GATHER, bool A_MN, bool B_GATHER, bool B_MN, int EPI, int EW, int GW, bool TG = false,
+          int DUAL = DUAL_NONE>
+__global__ void __launch_bounds__(threads(EW, GW, DUAL != 0), 1)
 grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                          const GemmParams p) {
+  // DUAL: four stages of three 16 KiB tiles (A, B and the second plain tile X) instead of six stages of two
+  constexpr int NSTAGES = DUAL != DUAL_NONE ? 4 : STAGES;
+  constexpr int X_STAGE_BYTES = DUAL != DUAL_NONE ? A_STAGE_BYTES : 0;
+  static_assert(DUAL != DUAL_N || !B_GATHER, "DUAL_N doubles the plain B tile");
+  static_assert(DUAL != DUAL_M || (!A_GATHER && A_MN && RAGGED_K), "DUAL_M doubles the plain MN-major A tile of a ragged-K kernel");
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sA = smem;
-  uint8_t* sB = smem + STAGES * A_STAGE_BYTES;
-  SharedStorage& ss = *reinterpret_cast<SharedStorage*>(smem + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES));
+  uint8_t* sB = smem + NSTAGES * A_STAGE_BYTES;
+  uint8_t* sX = sB + NSTAGES * B_STAGE_BYTES;
+  SharedStorage& ss = *reinterpret_cast<SharedStorage*>(smem + NSTAGES * (A_STAGE_BYTES + B_STAGE_BYTES + X_STAGE_BYTES));
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -115,7 +137,8 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
   const long long first_tile = blockIdx.x >> 1;
   const long long tile_step = gridDim.x >> 1;
   volatile int* abort_flag = &ss.abort_flag;
-  const int num_n = (p.N + BN - 1) / BN;
+  constexpr int UNIT_N = DUAL == DUAL_N ? 2 * BN : BN;
+  const int num_n = (p.N + UNIT_N - 1) / UNIT_N;
 
   constexpr bool kGather = A_GATHER || B_GATHER;
   static_assert(!(A_GATHER && B_GATHER), "at most one operand is gathered");
@@ -123,14 +146,16 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
   static_assert(EW == 4 || EW == 8, "4 or 8 epilogue warps");
   static_assert(GW == 0 || GW == 4 || GW == 8 || GW == 16, "0, 4, 8 or 16 gather warps");
   constexpr int GATHER_THREADS = 32 * GW;
-  constexpr int FIRST_GATHER_WARP = 2 + EW;
+  constexpr int FIRST_EPI_WARP = DUAL != DUAL_NONE ? 4 : 2;
+  constexpr int FIRST_GATHER_WARP = FIRST_EPI_WARP + EW;
+  static_assert(DUAL == DUAL_NONE || (EW == 8 && GW == 4), "dual tiles: 8 epilogue warps, 4 gather warps (512 threads)");
   constexpr bool kLsuGather = kGather && !TG;  // gathered bytes arrive through cp.async (not counted as tx bytes)
   constexpr uint32_t kTmaBytesPerCta =
-      (A_GATHER && !TG ? 0 : A_STAGE_BYTES) + (B_GATHER && !TG ? 0 : B_STAGE_BYTES);
+      (A_GATHER && !TG ? 0 : A_STAGE_BYTES) + (B_GATHER && !TG ? 0 : B_STAGE_BYTES) + X_STAGE_BYTES;
 
   // ---- set-up -------------------------------------------------------------------------------
   if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) {
+    for (int s = 0; s < NSTAGES; ++s) {
       mbar_init(smem_u32(&ss.full[s]), 1 + (kLsuGather ? 1 : 0));
       mbar_init(smem_u32(&ss.gfull[s]), kLsuGather ? GATHER_THREADS : 1);
       mbar_init(smem_u32(&ss.empty[s]), 1);
@@ -175,6 +200,11 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
   tc_fence_after();
   const uint32_t tmem_base = ss.tmem_base;
 
+  // DUAL: the epilogue warps hold 128 accumulator values per thread; registers move to them from the other roles
+  // (512 threads x 128 registers at launch; two warpgroups give up 72 registers per thread, two take 72).  Each
+  // role branch starts with its own setmaxnreg so that the register limit is known along the whole branch.
+  if (warp < FIRST_EPI_WARP) {
+  if constexpr (DUAL != DUAL_NONE) asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
   // ---- TMA producer -------------------------------------------------------------------------
   if (warp == 0) {
     if constexpr (kTmaBytesPerCta > 0) {
@@ -182,7 +212,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       uint32_t phase = 0;
       bool ok = true;
       Tile tile;
-      for (long long t = first_tile; ok && decode_tile<RAGGED_K>(p, ss, t, num_n, rank, tile); t += tile_step) {
+      for (long long t = first_tile; ok && decode_tile<RAGGED_K, DUAL>(p, ss, t, num_n, rank, tile); t += tile_step) {
         for (int kb = 0; kb < tile.num_kb; ++kb) {
           if (!mbar_wait(smem_u32(&ss.empty[stage]), phase ^ 1u, abort_flag)) { ok = false; break; }
           const uint32_t bar = map_to_cta(smem_u32(&ss.full[stage]), 0);  // the leader's barrier
@@ -207,7 +237,22 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
               if (lane < BN_CTA / 64) tma_load_2d_pair(&tmB, bar, b_dst + lane * CHUNK_BYTES, nb + 64 * lane, krow);
             }
           }
-          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+          if constexpr (DUAL == DUAL_N) {  // the unit's second B tile: columns n0 + 256 ...
+            const uint32_t x_dst = smem_u32(sX + stage * X_STAGE_BYTES);
+            const int nb = tile.n0 + BN + static_cast<int>(rank) * BN_CTA;
+            if constexpr (!B_MN) {
+              if (lane == 0) tma_load_2d_pair(&tmB, bar, x_dst, k0, tile.e * p.b_rows_per_expert + nb);
+            } else {
+              const int krow = RAGGED_K ? k0 : (tile.e * p.b_rows_per_expert + k0);
+              if (lane < BN_CTA / 64) tma_load_2d_pair(&tmB, bar, x_dst + lane * CHUNK_BYTES, nb + 64 * lane, krow);
+            }
+          }
+          if constexpr (DUAL == DUAL_M) {  // the unit's second A tile: rows row0 + 256 ...
+            const uint32_t x_dst = smem_u32(sX + stage * X_STAGE_BYTES);
+            if (lane < BM / 64)
+              tma_load_2d_pair(&tmA, bar, x_dst + lane * CHUNK_BYTES, tile.row0 + 2 * BM + 64 * lane, k0);
+          }
+          if (++stage == NSTAGES) { stage = 0; phase ^= 1u; }
         }
       }
       if (!ok && lane == 0 && p.status) atomicCAS(p.status, ST_OK, ST_TIMEOUT_PRODUCER);
@@ -227,35 +272,75 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       uint32_t acc_phase = 0;
       bool ok = true;
       Tile tile;
-      for (long long t = first_tile; ok && decode_tile<RAGGED_K>(p, ss, t, num_n, rank, tile); t += tile_step) {
+      for (long long t = first_tile; ok && decode_tile<RAGGED_K, DUAL>(p, ss, t, num_n, rank, tile); t += tile_step) {
         if (tile.num_kb == 0) continue;
-        if (!mbar_wait(smem_u32(&ss.acc_empty[acc]), acc_phase ^ 1u, abort_flag)) { ok = false; break; }
+        if constexpr (DUAL == DUAL_NONE) {
+          if (!mbar_wait(smem_u32(&ss.acc_empty[acc]), acc_phase ^ 1u, abort_flag)) { ok = false; break; }
+        } else {
+          // both accumulators belong to this unit; the first group may start as soon as the epilogue has copied the
+          // previous unit's first accumulator out, the second group waits for the second one (below)
+          if (!mbar_wait(smem_u32(&ss.acc_empty[0]), acc_phase ^ 1u, abort_flag)) { ok = false; break; }
+        }
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * BN;
+        const uint32_t d_tmem = tmem_base + (DUAL == DUAL_NONE ? acc * BN : 0);
         for (int kb = 0; kb < tile.num_kb; ++kb) {
           if (!mbar_wait(smem_u32(&ss.full[stage]), phase, abort_flag)) { ok = false; break; }
           if constexpr (kLsuGather) {
             if (!mbar_wait(smem_u32(&ss.gfull[stage]), phase, abort_flag)) { ok = false; break; }
           }
           tc_fence_after();
+          const uint64_t a_desc = make_smem_desc(smem_u32(sA + stage * A_STAGE_BYTES), a_lbo, 1024);
+          const uint64_t b_desc = make_smem_desc(smem_u32(sB + stage * B_STAGE_BYTES), b_lbo, 1024);
           if (lane == 0) {
             if constexpr (kLsuGather) fence_proxy_async_smem();
-            const uint64_t a_desc = make_smem_desc(smem_u32(sA + stage * A_STAGE_BYTES), a_lbo, 1024);
-            const uint64_t b_desc = make_smem_desc(smem_u32(sB + stage * B_STAGE_BYTES), b_lbo, 1024);
 #pragma unroll
             for (int k4 = 0; k4 < BK / UMMA_K; ++k4) {
               umma_bf16_pair(d_tmem, a_desc + ((k4 * a_kstep) >> 4), b_desc + ((k4 * b_kstep) >> 4), idesc,
                              (kb > 0 || k4 > 0) ? 1u : 0u);
             }
+          }
+          if constexpr (DUAL != DUAL_NONE) {
+            if (kb == 0) {  // the second accumulator of the previous unit has been copied out
+              __syncwarp();
+              if (!mbar_wait(smem_u32(&ss.acc_empty[1]), acc_phase ^ 1u, abort_flag)) { ok = false; break; }
+              tc_fence_after();
+            }
+          }
+          if (lane == 0) {
+            if constexpr (DUAL == DUAL_N) {
+              const uint64_t x_desc = make_smem_desc(smem_u32(sX + stage * X_STAGE_BYTES), b_lbo, 1024);
+#pragma unroll
+              for (int k4 = 0; k4 < BK / UMMA_K; ++k4) {
+                umma_bf16_pair(d_tmem + BN, a_desc + ((k4 * a_kstep) >> 4), x_desc + ((k4 * b_kstep) >> 4), idesc,
+                               (kb > 0 || k4 > 0) ? 1u : 0u);
+              }
+            }
+            if constexpr (DUAL == DUAL_M) {
+              const uint64_t x_desc = make_smem_desc(smem_u32(sX + stage * X_STAGE_BYTES), a_lbo, 1024);
+#pragma unroll
+              for (int k4 = 0; k4 < BK / UMMA_K; ++k4) {
+                umma_bf16_pair(d_tmem + BN, x_desc + ((k4 * a_kstep) >> 4), b_desc + ((k4 * b_kstep) >> 4), idesc,
+                               (kb > 0 || k4 > 0) ? 1u : 0u);
+              }
+            }
             umma_commit_pair(smem_u32(&ss.empty[stage]), 3);  // frees the stage in both CTAs
           }
           __syncwarp();
-          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+          if (++stage == NSTAGES) { stage = 0; phase ^= 1u; }
         }
         if (!ok) break;
-        if (lane == 0) umma_commit_pair(smem_u32(&ss.acc_full[acc]), 3);
-        __syncwarp();
-        if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+        if constexpr (DUAL == DUAL_NONE) {
+          if (lane == 0) umma_commit_pair(smem_u32(&ss.acc_full[acc]), 3);
+          __syncwarp();
+          if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+        } else {
+          if (lane == 0) {
+            umma_commit_pair(smem_u32(&ss.acc_full[0]), 3);
+            umma_commit_pair(smem_u32(&ss.acc_full[1]), 3);
+          }
+          __syncwarp();
+          acc_phase ^= 1u;
+        }
       }
       if (!ok && lane == 0 && p.status) atomicCAS(p.status, ST_OK, ST_TIMEOUT_MMA);
     } else {
@@ -268,7 +353,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         uint32_t phase = 0;
         bool ok = true;
         Tile tile;
-        for (long long t = first_tile; ok && decode_tile<RAGGED_K>(p, ss, t, num_n, rank, tile); t += tile_step) {
+        for (long long t = first_tile; ok && decode_tile<RAGGED_K, DUAL>(p, ss, t, num_n, rank, tile); t += tile_step) {
           for (int kb = 0; kb < tile.num_kb; ++kb) {
             if (!mbar_wait(smem_u32(&ss.gfull[stage]), phase, abort_flag)) { ok = false; break; }
             if (lane == 0) {
@@ -276,15 +361,17 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
               mbar_arrive_cluster_relaxed(map_to_cta(smem_u32(&ss.full[stage]), 0));
             }
             __syncwarp();
-            if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+            if (++stage == NSTAGES) { stage = 0; phase ^= 1u; }
           }
         }
         if (!ok && lane == 0 && p.status) atomicCAS(p.status, ST_OK, ST_TIMEOUT_MMA);
       }
     }
   }
+  }  // warps below FIRST_EPI_WARP (DUAL: warps 2 and 3 idle)
   // ---- gather producers ----------------------------------------------------------------------
   else if (warp >= FIRST_GATHER_WARP) {
+    if constexpr (DUAL != DUAL_NONE) asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
     if constexpr (kGather) {
       const int gt = threadIdx.x - 32 * FIRST_GATHER_WARP;
       int stage = 0;
@@ -300,7 +387,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         const CUtensorMap* tm = A_GATHER ? &tmA : &tmB;
         uint8_t* stage_base = A_GATHER ? sA : sB;
         constexpr int STAGE_BYTES = A_GATHER ? A_STAGE_BYTES : B_STAGE_BYTES;
-        for (long long t = first_tile; ok && decode_tile<RAGGED_K>(p, ss, t, num_n, rank, tile); t += tile_step) {
+        for (long long t = first_tile; ok && decode_tile<RAGGED_K, DUAL>(p, ss, t, num_n, rank, tile); t += tile_step) {
           if constexpr (!RAGGED_K) {
             int r4[4];
 #pragma unroll
@@ -314,7 +401,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
                 tma_gather4_pair(tm, map_to_cta(smem_u32(&ss.full[stage]), 0),
                                  smem_u32(stage_base + stage * STAGE_BYTES) + j * 512, kb * BK, r4[0], r4[1], r4[2],
                                  r4[3]);
-              if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+              if (++stage == NSTAGES) { stage = 0; phase ^= 1u; }
             }
           } else {
             const int chunk = j >> 4, tq = j & 15;  // 2 chunks of 64 columns, 16 groups of 4 tokens
@@ -338,12 +425,12 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
 #pragma unroll
               for (int i = 0; i < 4; ++i) cur[i] = nxt[i];
               load_idx(kb + 2, nxt);
-              if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+              if (++stage == NSTAGES) { stage = 0; phase ^= 1u; }
             }
           }
         }
       } else
-      for (long long t = first_tile; ok && decode_tile<RAGGED_K>(p, ss, t, num_n, rank, tile); t += tile_step) {
+      for (long long t = first_tile; ok && decode_tile<RAGGED_K, DUAL>(p, ss, t, num_n, rank, tile); t += tile_step) {
         if constexpr (!RAGGED_K) {
           // K-major A: 128 rows x 128 B; 8 consecutive threads fetch the 8 pieces of a row
           static_assert(RAGGED_K || (A_GATHER && !A_MN), "ragged-M kernels gather a K-major A");
@@ -364,7 +451,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
 #pragma unroll
             for (int i = 0; i < NPASS; ++i) cp_async16(dst + i * (RPP * 128), src[i] + kb * BK, 16);
             cp_async_arrive_noinc(smem_u32(&ss.gfull[stage]));
-            if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+            if (++stage == NSTAGES) { stage = 0; phase ^= 1u; }
           }
         } else {
           // MN-major: one token per 128-byte row; this CTA stages 128 elements of M (A) or N (B) = 2 chunks,
@@ -407,7 +494,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
 #pragma unroll
             for (int i = 0; i < PASSES; ++i) { idx0[i] = idx1[i]; idx1[i] = idx2[i]; }
             load_idx(kb + 3, idx2);
-            if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+            if (++stage == NSTAGES) { stage = 0; phase ^= 1u; }
           }
         }
       }
@@ -417,60 +504,100 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
   }
   // ---- epilogue -----------------------------------------------------------------------------
   else {
+    if constexpr (DUAL != DUAL_NONE) asm volatile("setmaxnreg.inc.sync.aligned.u32 200;");
     const int quad = warp & 3;
     constexpr int COL_SPLIT = EW / 4;
     constexpr int COLS_PER_WARP = BN / COL_SPLIT;
-    const int col_half = (warp - 2) >> 2;
+    const int col_half = (warp - FIRST_EPI_WARP) >> 2;
     const int row_in_tile = quad * 32 + lane;
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
     Tile tile;
-    for (long long t = first_tile; ok && decode_tile<RAGGED_K>(p, ss, t, num_n, rank, tile); t += tile_step) {
-      const int r = tile.row0 + row_in_tile;
-      const bool row_ok = r < tile.row_end;
+    for (long long t = first_tile; ok && decode_tile<RAGGED_K, DUAL>(p, ss, t, num_n, rank, tile); t += tile_step) {
       const bool have_acc = tile.num_kb > 0;
-      if (have_acc) {
-        if (!mbar_wait(smem_u32(&ss.acc_full[acc]), acc_phase, abort_flag)) { ok = false; break; }
-        tc_fence_after();
-      }
-      float score = 0.f;
-      if constexpr (EPI == EPI_DSWIGLU || EPI == EPI_DACT || EPI == EPI_SCATTER) {
-        if (row_ok) score = load_score(p.scores, p.scores_are_bf16, p.s_scatter[r]);
-      }
-      float ds_acc = 0.f;
-      const uint32_t t_addr = tmem_base + acc * BN + (static_cast<uint32_t>(quad * 32) << 16);
+      constexpr int SUBTILES = DUAL == DUAL_NONE ? 1 : 2;
 #pragma unroll 1
-      for (int c = col_half * (COLS_PER_WARP / 32); c < (col_half + 1) * (COLS_PER_WARP / 32); ++c) {
-        const int n = tile.n0 + c * 32;
-        if (n >= p.N) break;
-        uint32_t v[32];
-        if (have_acc) {
-          tmem_ld32(t_addr + c * 32, v);
-          tmem_ld_wait();
-        } else {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = 0u;
+      for (int sub = 0; sub < SUBTILES && ok; ++sub) {
+        if constexpr (DUAL != DUAL_NONE) acc = sub;
+        const int r = tile.row0 + (DUAL == DUAL_M ? sub * 2 * BM : 0) + row_in_tile;
+        const int n0 = tile.n0 + (DUAL == DUAL_N ? sub * BN : 0);
+        const bool row_ok = r < tile.row_end;
+        float score = 0.f;
+        if constexpr (EPI == EPI_DSWIGLU || EPI == EPI_DACT || EPI == EPI_SCATTER) {
+          if (row_ok) score = load_score(p.scores, p.scores_are_bf16, p.s_scatter[r]);
         }
-        if (!row_ok) continue;
-        epilogue_chunk<EPI, RAGGED_K>(p, tile.e, r, n, v, score, ds_acc);
-      }
-      if constexpr (EPI == EPI_DSWIGLU || EPI == EPI_DACT) {
-        if (row_ok) {
-          float* dsp = p.ds_partial + static_cast<long long>(2 * (tile.n0 / BN)) * p.total_rows + r;
-          if constexpr (COL_SPLIT == 2) {
-            dsp[static_cast<long long>(col_half) * p.total_rows] = ds_acc;
+        if (have_acc) {
+          if (!mbar_wait(smem_u32(&ss.acc_full[acc]), acc_phase, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+        }
+        float ds_acc = 0.f;
+        const uint32_t t_addr = tmem_base + acc * BN + (static_cast<uint32_t>(quad * 32) << 16);
+        if constexpr (DUAL != DUAL_NONE) {
+          // Copy this warp's columns of the accumulator into registers and hand the accumulator back at once: the
+          // next unit's MMAs need both accumulators, so the epilogue arithmetic and stores must not hold them.
+          static_assert(DUAL == DUAL_NONE || COLS_PER_WARP == 128, "dual tiles use 8 epilogue warps");
+          constexpr int CHUNKS = COLS_PER_WARP / 32;
+          uint32_t v[CHUNKS][32];
+          if (have_acc) {
+#pragma unroll
+            for (int c = 0; c < CHUNKS; ++c) tmem_ld32(t_addr + (col_half * CHUNKS + c) * 32, v[c]);
+            tmem_ld_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster_relaxed(map_to_cta(smem_u32(&ss.acc_empty[acc]), 0));
           } else {
-            dsp[0] = ds_acc;
-            dsp[p.total_rows] = 0.f;
+#pragma unroll
+            for (int c = 0; c < CHUNKS; ++c)
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[c][j] = 0u;
+          }
+          if (row_ok) {
+#pragma unroll
+            for (int c = 0; c < CHUNKS; ++c) {
+              const int n = n0 + (col_half * CHUNKS + c) * 32;
+              if (n < p.N) epilogue_chunk<EPI, RAGGED_K>(p, tile.e, r, n, v[c], score, ds_acc);
+            }
+          }
+        } else {
+#pragma unroll 1
+          for (int c = col_half * (COLS_PER_WARP / 32); c < (col_half + 1) * (COLS_PER_WARP / 32); ++c) {
+            const int n = n0 + c * 32;
+            if (n >= p.N) break;
+            uint32_t v[32];
+            if (have_acc) {
+              tmem_ld32(t_addr + c * 32, v);
+              tmem_ld_wait();
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] = 0u;
+            }
+            if (!row_ok) continue;
+            epilogue_chunk<EPI, RAGGED_K>(p, tile.e, r, n, v, score, ds_acc);
+          }
+        }
+        if constexpr (EPI == EPI_DSWIGLU || EPI == EPI_DACT) {
+          if (row_ok && n0 < p.N) {
+            float* dsp = p.ds_partial + static_cast<long long>(2 * (n0 / BN)) * p.total_rows + r;
+            if constexpr (COL_SPLIT == 2) {
+              dsp[static_cast<long long>(col_half) * p.total_rows] = ds_acc;
+            } else {
+              dsp[0] = ds_acc;
+              dsp[p.total_rows] = 0.f;
+            }
+          }
+        }
+        if constexpr (DUAL == DUAL_NONE) {
+          if (have_acc) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&ss.acc_empty[acc]), 0));
+            if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
           }
         }
       }
-      if (have_acc) {
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&ss.acc_empty[acc]), 0));
-        if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+      if constexpr (DUAL != DUAL_NONE) {
+        if (have_acc) acc_phase ^= 1u;
       }
     }
     if (!ok && lane == 0 && p.status) atomicCAS(p.status, ST_OK, ST_TIMEOUT_EPILOGUE);
