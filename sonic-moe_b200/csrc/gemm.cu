@@ -167,7 +167,11 @@ static int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const Gem
     if (use_tma_gather_pair()) {
       // (not for the activation-gradient epilogues: they are long enough that losing the overlap of epilogue and
       // main loop costs more than the halved gather traffic gains: 2.3-2.5 ms against 2.2 ms)
-      if (use_dual_tiles() && EPI != EPI_DSWIGLU && EPI != EPI_DACT) {
+      // nor when the doubled dimension is so far from a multiple of 512 that the half-empty last unit wastes more
+      // than an eighth of the MMA work (e.g. N = 768)
+      const int doubled = A_GATHER ? p.N : p.M;
+      const bool fits = ((doubled + 511) / 512 * 512 - doubled) * 8 <= doubled;
+      if (use_dual_tiles() && fits && EPI != EPI_DSWIGLU && EPI != EPI_DACT) {
         constexpr int kDual = A_GATHER ? pair::DUAL_N : pair::DUAL_M;
         return launch_pair_variant<RAGGED_K, A_GATHER, A_MN, B_GATHER, B_MN, EPI, 8, 4, true, kDual>(tmA, tmB, p, stream);
       }
