@@ -211,13 +211,15 @@ grouped_gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
       uint32_t set_phase = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      Tile tile;
-      for (long long t = first_tile; ok && fp8::decode_tile(p, ss, t, num_n, rank, tile); t += tile_step) {
+      // the issuer only needs the number of work units and of k-blocks (a constant): no per-tile decode on its path
+      const long long total_units = static_cast<long long>(ss.m_tile_prefix[p.E]) * num_n;
+      const int num_kb = p.K / BK;
+      for (long long t = first_tile; ok && t < total_units; t += tile_step) {
         // the epilogue warps of both CTAs have copied the previous tile out of tensor memory
         if (!mbar_wait(smem_u32(&ss.acc_empty), acc_phase ^ 1u, abort_flag)) { ok = false; break; }
         acc_phase ^= 1u;
         uint32_t tsfa = 0, tsfb = 0;
-        for (int kb = 0; kb < tile.num_kb; ++kb) {
+        for (int kb = 0; kb < num_kb; ++kb) {
           if ((kb & (KB_PER_GROUP - 1)) == 0) {
             if (!mbar_wait(smem_u32(&ss.sf_full[set]), set_phase, abort_flag)) { ok = false; break; }
             tc_fence_after();
@@ -244,7 +246,7 @@ grouped_gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
               umma_mx_pair(tmem_base, a_desc + ((k4 * UMMA_K) >> 4), b_desc + ((k4 * b_kstep) >> 4), idesc, tsfa,
                            tsfb, (kb > 0 || k4 > 0) ? 1u : 0u);
             umma_commit_pair(smem_u32(&ss.empty[stage]), 3);
-            if (kb == tile.num_kb - 1) umma_commit_pair(smem_u32(&ss.acc_full), 3);
+            if (kb == num_kb - 1) umma_commit_pair(smem_u32(&ss.acc_full), 3);
           }
           __syncwarp();
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }

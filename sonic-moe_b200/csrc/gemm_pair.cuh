@@ -111,6 +111,34 @@ __device__ __forceinline__ bool decode_tile(const GemmParams& p, const SharedSto
   }
 }
 
+// What the MMA issuer needs to know about work unit t: whether it exists and how many k-blocks it has.  The full
+// decode_tile (a 64-bit division, a binary search and two dependent global loads) would sit between the last MMA of
+// one tile and the first of the next; for ragged-M the k-block count is a constant, for ragged-K the expert's token
+// range is fetched one unit ahead by the caller.
+template <bool RAGGED_K, int DUAL>
+__device__ __forceinline__ long long num_units(const GemmParams& p, const SharedStorage& ss, int num_n) {
+  if constexpr (!RAGGED_K) {
+    return static_cast<long long>(ss.m_tile_prefix[p.E]) * num_n;
+  } else {
+    constexpr int UNIT_M = DUAL == DUAL_M ? 4 * BM : 2 * BM;
+    const int num_m = (p.M + UNIT_M - 1) / UNIT_M;
+    return static_cast<long long>(num_m) * num_n * p.E;
+  }
+}
+
+template <bool RAGGED_K, int DUAL>
+__device__ __forceinline__ int unit_num_kb(const GemmParams& p, long long t, long long total, int num_n) {
+  if (t >= total) return 0;
+  if constexpr (!RAGGED_K) {
+    return p.K / BK;
+  } else {
+    constexpr int UNIT_M = DUAL == DUAL_M ? 4 * BM : 2 * BM;
+    const int num_m = (p.M + UNIT_M - 1) / UNIT_M;
+    const int e = static_cast<int>(t / (static_cast<long long>(num_m) * num_n));
+    return (p.off[e + 1] - p.off[e] + BK - 1) / BK;
+  }
+}
+
 // TG: the gather warps fetch rows with TMA tile::gather4 (32 issuing threads spread over the gather warps)
 // instead of 16-byte cp.async copies; completion then goes straight to the leader's full barrier.
 template <bool RAGGED_K, bool A_GATHER, bool A_MN, bool B_GATHER, bool B_MN, int EPI, int EW, int GW, bool TG = false,
@@ -271,9 +299,12 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      Tile tile;
-      for (long long t = first_tile; ok && decode_tile<RAGGED_K, DUAL>(p, ss, t, num_n, rank, tile); t += tile_step) {
-        if (tile.num_kb == 0) continue;
+      const long long total_units = num_units<RAGGED_K, DUAL>(p, ss, num_n);
+      int next_kb = unit_num_kb<RAGGED_K, DUAL>(p, first_tile, total_units, num_n);
+      for (long long t = first_tile; ok && t < total_units; t += tile_step) {
+        const int num_kb = next_kb;
+        next_kb = unit_num_kb<RAGGED_K, DUAL>(p, t + tile_step, total_units, num_n);  // loads overlap this unit's MMAs
+        if (num_kb == 0) continue;
         if constexpr (DUAL == DUAL_NONE) {
           if (!mbar_wait(smem_u32(&ss.acc_empty[acc]), acc_phase ^ 1u, abort_flag)) { ok = false; break; }
         } else {
@@ -283,7 +314,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (DUAL == DUAL_NONE ? acc * BN : 0);
-        for (int kb = 0; kb < tile.num_kb; ++kb) {
+        for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(smem_u32(&ss.full[stage]), phase, abort_flag)) { ok = false; break; }
           if constexpr (kLsuGather) {
             if (!mbar_wait(smem_u32(&ss.gfull[stage]), phase, abort_flag)) { ok = false; break; }
