@@ -351,3 +351,43 @@ def test_kernels_are_deterministic(smoe):
                                        T, H, I, E, T * K, st.data_ptr(), stream)
         outs.append((z, y1))
     assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
+
+
+_DUAL_SNIPPET = """
+import sys, torch
+sys.path.insert(0, {root!r}); sys.path.insert(0, {pkg!r})
+from oracle import moe_oracle as orc
+from sonicmoe import MoE, _lib
+from sonicmoe.enums import ActivationType
+T, H, I, E, K = 2048, 1024, 512, 8, 2
+inp = orc.make_inputs(T, H, I, E, K, seed=5, dtype=torch.bfloat16, w_std=0.05)
+moe = MoE(E, K, H, I, ActivationType.SWIGLU, False, 0.02).cuda().bfloat16()
+with torch.no_grad():
+    moe.router.weight.copy_(inp["router_w"]); moe.c_fc.weight.copy_(inp["w1"]); moe.c_proj.weight.copy_(inp["w2"])
+x = inp["x"].cuda().requires_grad_(True)
+o, _ = moe(x)
+o.backward(inp["dout"].cuda())
+torch.cuda.synchronize(); _lib.check_status()
+torch.save({{"o": o.detach().cpu(), "dx": x.grad.cpu(), "dw1": moe.c_fc.weight.grad.cpu(),
+            "dw2": moe.c_proj.weight.grad.cpu()}}, {out!r})
+"""
+
+
+def test_dual_tiles_match_single_tiles(smoe, tmp_path):
+    """The two-tiles-per-gathered-stage kernels accumulate every tile in the same order as the single-tile kernels:
+    layer outputs and all gradients must be bit-identical with SMOE_DUAL=1 (default) and SMOE_DUAL=0."""
+    import os
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    pkg = os.path.join(root, "sonic-moe_b200")
+    results = {}
+    for dual in ("1", "0"):
+        out = str(tmp_path / f"dual{dual}.pt")
+        env = dict(os.environ, SMOE_DUAL=dual)
+        subprocess.run([sys.executable, "-c", _DUAL_SNIPPET.format(root=root, pkg=pkg, out=out)], check=True, env=env,
+                       timeout=300)
+        results[dual] = torch.load(out)
+    for name in ("o", "dx", "dw1", "dw2"):
+        assert torch.equal(results["1"][name], results["0"][name]), name
