@@ -70,9 +70,10 @@ static int num_sms() {
   return sms;
 }
 
-// Gathered operands are fetched by cp.async warps (default) or, with SMOE_TMA_GATHER=1 in the
-// environment, by TMA tile::gather4 from the producer warp.  SMOE_EPI_WARPS (4|8) and
-// SMOE_GATHER_WARPS (4|8) override the per-kernel warp counts (for tuning runs).
+// Gathered operands: the CTA-pair kernels fetch them by TMA tile::gather4 issued from 32 threads spread over the
+// gather warps (SMOE_TMA_GATHER=0: 16-byte cp.async copies instead); the single-CTA kernels use cp.async warps
+// (SMOE_TMA_GATHER=1: gather4 from the producer warp).  SMOE_EPI_WARPS (4|8) and SMOE_GATHER_WARPS (4|8) override
+// the per-kernel warp counts of the single-tile kernels (for tuning runs).
 static int env_int(const char* name, int dflt) {
   const char* e = getenv(name);
   return (e != nullptr && e[0] != 0) ? atoi(e) : dflt;
