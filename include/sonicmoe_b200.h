@@ -149,6 +149,21 @@ int smoe_up_projection_forward(const void* x, const void* w1, void* z, void* y1,
 int smoe_down_projection_forward(const void* y1, const void* w2, void* y2, const int* expert_offset, int H, int I,
                                  int E, int TK, int* status, void* stream);
 
+/* Layers whose tokens have exactly one routed row each (top-1 routing; the rows an expert-parallel rank receives):
+ * the combine is a permutation, so the down projection writes o[x_gather_idx[r], :] = score[s_scatter_idx[r]] *
+ * bf16(y2[r, :]) directly (scores NULL = 1) and the dX GEMM writes dx[x_gather_idx[r], :] directly -- no y2 /
+ * dx_expanded buffer, no gather-and-sum pass.  Every row of o / dx is written exactly once when x_gather_idx is a
+ * permutation of 0..TK-1.  Same results, bit for bit, as smoe_down_projection_forward + smoe_gather_sum (K = 1) and
+ * smoe_up_projection_backward_dx + smoe_gather_sum (K = 1).  (Reference: the K = 1 case of _down_projection_forward +
+ * _router_forward, forward.py:132-202, and of _up_projection_backward + _token_broadcast_backward,
+ * backward.py:195-280, 464-484.) */
+int smoe_down_projection_forward_rows(const void* y1, const void* w2, void* o, const void* scores, int scores_are_bf16,
+                                      const int* expert_offset, const int* x_gather_idx, const int* s_scatter_idx,
+                                      int H, int I, int E, int TK, int* status, void* stream);
+int smoe_up_projection_backward_dx_rows(const void* dz, const void* w1, void* dx, const int* expert_offset,
+                                        const int* x_gather_idx, int H, int I, int E, int TK, int* status,
+                                        void* stream);
+
 /* Fused down projection + router-weighted scatter-reduce: o_acc[x_gather_idx[r], :] += score(r) * (y1[r] @ W2[e]^T)
  * with fp32 atomics; o_acc (T,H) fp32 must be zero on entry.  score(r) = scores[s_scatter_idx[r]].
  * Replaces _down_projection_forward followed by _router_forward (sonicmoe/functional/forward.py:132-202). */
@@ -283,6 +298,16 @@ int smoe_mxfp8_down_projection_backward_act(const void* doutq, const void* dout_
 int smoe_mxfp8_up_projection_backward_dx(const void* dzq, const void* dz_scale, const void* w1q, const void* w1_scale,
                                          void* dx_expanded, const int* expert_offset, int H, int I, int E, int TK,
                                          int* status, void* stream);
+/* The one-row-per-token forms (see smoe_down_projection_forward_rows) with FP8 operands. */
+int smoe_mxfp8_down_projection_forward_rows(const void* y1q, const void* y1_scale, const void* w2q,
+                                            const void* w2_scale, void* o, const void* scores, int scores_are_bf16,
+                                            const int* expert_offset, const int* x_gather_idx,
+                                            const int* s_scatter_idx, int H, int I, int E, int TK, int* status,
+                                            void* stream);
+int smoe_mxfp8_up_projection_backward_dx_rows(const void* dzq, const void* dz_scale, const void* w1q,
+                                              const void* w1_scale, void* dx, const int* expert_offset,
+                                              const int* x_gather_idx, int H, int I, int E, int TK, int* status,
+                                              void* stream);
 
 #ifdef __cplusplus
 }

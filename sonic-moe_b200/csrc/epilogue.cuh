@@ -14,6 +14,9 @@ enum Epilogue : int {
   EPI_ACT = 4,         // z = acc + b1 -> out0 (unless nullptr); y1 = act(z) (gated: act(z_even) * z_odd) -> out1
   EPI_DACT = 5,        // acc = dy1; reads z, score; writes dz (out0), y1*s (out1), per-row partial of ds
   EPI_STORE_BIAS = 6,  // out0[r, n] = bf16(acc + bias[e, n])
+  EPI_STORE_ROWS = 7,  // out0[gather[r], n] = bf16(score(r) * bf16(acc)) (score 1 when scores == nullptr): grouped rows
+                       // written straight back to their source rows -- the combine of a layer whose tokens have one
+                       // routed row each, with the rounding points of the store + gather_sum pair it replaces
 };
 
 // Activation codes (GemmParams::act).  The first three are gated: the pre-activation has 2I columns,
@@ -288,6 +291,16 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, int expert, 
       store_bf16x32(p.out0 + r * p.ld0 + n, dzf);
       store_bf16x32(p.out1 + r * p.ld1 + n, ysf);
     }
+  } else if constexpr (EPI == EPI_STORE_ROWS) {
+    __nv_bfloat16* dst = p.out0 + static_cast<long long>(p.gather[r]) * p.ld0 + n;
+    float f[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+    if (p.scores != nullptr) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) f[j] = score * __bfloat162float(__float2bfloat16_rn(f[j]));
+    }
+    store_bf16x32(dst, f);
   } else if constexpr (EPI == EPI_SCATTER) {
     float* dst = p.acc_out + static_cast<long long>(p.gather[r]) * p.N + n;
 #pragma unroll

@@ -266,6 +266,24 @@ int smoe_down_projection_forward(const void* y1, const void* w2, void* y2, const
   return launch<false, false, false, false, false, EPI_STORE>(tmA, tmB, p, static_cast<cudaStream_t>(stream), 4, 0);
 }
 
+int smoe_down_projection_forward_rows(const void* y1, const void* w2, void* o, const void* scores, int scores_are_bf16,
+                                      const int* expert_offset, const int* x_gather_idx, const int* s_scatter_idx,
+                                      int H, int I, int E, int TK, int* status, void* stream) {
+  if (bad_shape(H, I, E) || TK < 0) return SMOE_ERR_SHAPE;
+  if (TK == 0) return SMOE_OK;
+  if (x_gather_idx == nullptr || (scores != nullptr && s_scatter_idx == nullptr)) return SMOE_ERR_SHAPE;
+  CUtensorMap tmA, tmB;
+  SMOE_TRY(encode_2d(&tmA, y1, TK, I, I, BM, BK));
+  SMOE_TRY(encode_2d(&tmB, w2, (uint64_t)E * H, I, I, use_cta_pair() ? pair::BN_CTA : BN, BK));
+  GemmParams p = {};
+  p.E = E; p.N = H; p.K = I; p.total_rows = TK; p.b_rows_per_expert = H;
+  p.off = expert_offset; p.gather = x_gather_idx; p.s_scatter = s_scatter_idx;
+  p.scores = scores; p.scores_are_bf16 = scores_are_bf16;
+  p.out0 = static_cast<__nv_bfloat16*>(o); p.ld0 = H;
+  p.status = status;
+  return launch<false, false, false, false, false, EPI_STORE_ROWS>(tmA, tmB, p, static_cast<cudaStream_t>(stream), 4, 0);
+}
+
 int smoe_down_projection_forward_scatter(const void* y1, const void* w2, float* o_acc, const void* scores,
                                          int scores_are_bf16, const int* expert_offset, const int* x_gather_idx,
                                          const int* s_scatter_idx, int T, int H, int I, int E, int TK, int* status,
@@ -385,6 +403,22 @@ int smoe_up_projection_backward_dx(const void* dz, const void* w1, void* dx_expa
   p.out0 = static_cast<__nv_bfloat16*>(dx_expanded); p.ld0 = H;
   p.status = status;
   return launch<false, false, false, false, true, EPI_STORE>(tmA, tmB, p, static_cast<cudaStream_t>(stream), 4, 0);
+}
+
+int smoe_up_projection_backward_dx_rows(const void* dz, const void* w1, void* dx, const int* expert_offset,
+                                        const int* x_gather_idx, int H, int I, int E, int TK, int* status,
+                                        void* stream) {
+  if (bad_shape(H, I, E) || TK < 0 || x_gather_idx == nullptr) return SMOE_ERR_SHAPE;
+  if (TK == 0) return SMOE_OK;
+  CUtensorMap tmA, tmB;
+  SMOE_TRY(encode_2d(&tmA, dz, TK, 2 * I, 2 * I, BM, BK));
+  SMOE_TRY(encode_2d(&tmB, w1, (uint64_t)E * 2 * I, H, H, BK, 64));    // W1[e] (2I, H): rows are k, MN-major
+  GemmParams p = {};
+  p.E = E; p.N = H; p.K = 2 * I; p.total_rows = TK; p.b_rows_per_expert = 2 * I;
+  p.off = expert_offset; p.gather = x_gather_idx;
+  p.out0 = static_cast<__nv_bfloat16*>(dx); p.ld0 = H;
+  p.status = status;
+  return launch<false, false, false, false, true, EPI_STORE_ROWS>(tmA, tmB, p, static_cast<cudaStream_t>(stream), 4, 0);
 }
 
 int smoe_down_projection_weight_grad(const void* dout, const void* y1s, void* dw2, const int* expert_offset,

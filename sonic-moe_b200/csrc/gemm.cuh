@@ -389,8 +389,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       }
       float score = 0.f;
       int slot = 0;
-      if constexpr (EPI == EPI_DSWIGLU || EPI == EPI_SCATTER) {
-        if (row_ok) {
+      if constexpr (EPI == EPI_DSWIGLU || EPI == EPI_SCATTER || EPI == EPI_STORE_ROWS) {
+        if (row_ok && (EPI != EPI_STORE_ROWS || p.scores != nullptr)) {
           slot = p.s_scatter[r];
           score = load_score(p.scores, p.scores_are_bf16, slot);
         }

@@ -409,6 +409,45 @@ int smoe_mxfp8_down_projection_forward(const void* y1q, const void* y1_scale, co
   return launch_mx<false, false, EPI_STORE>(tmA, tmB, p, sc, static_cast<cudaStream_t>(stream));
 }
 
+int smoe_mxfp8_down_projection_forward_rows(const void* y1q, const void* y1_scale, const void* w2q,
+                                            const void* w2_scale, void* o, const void* scores, int scores_are_bf16,
+                                            const int* expert_offset, const int* x_gather_idx,
+                                            const int* s_scatter_idx, int H, int I, int E, int TK, int* status,
+                                            void* stream) {
+  if (bad_shape(H, I, E) || TK < 0) return SMOE_ERR_SHAPE;
+  if (TK == 0) return SMOE_OK;
+  if (x_gather_idx == nullptr || (scores != nullptr && s_scatter_idx == nullptr)) return SMOE_ERR_SHAPE;
+  CUtensorMap tmA, tmB;
+  SMOE_TRY(encode_u8(&tmA, y1q, TK, I, BM, BK));
+  SMOE_TRY(encode_u8(&tmB, w2q, (uint64_t)E * H, I, BN_CTA, BK));
+  GemmParams p = {};
+  p.E = E; p.N = H; p.K = I; p.total_rows = TK; p.b_rows_per_expert = H;
+  p.off = expert_offset; p.gather = x_gather_idx; p.s_scatter = s_scatter_idx;
+  p.scores = scores; p.scores_are_bf16 = scores_are_bf16;
+  p.out0 = static_cast<__nv_bfloat16*>(o); p.ld0 = H;
+  p.status = status;
+  const mx8::ScaleBytes sc = mx_scales(y1_scale, I, w2_scale, (long long)(H / 128) * (I / 128), I / 128, 1);
+  return launch_mx<false, false, EPI_STORE_ROWS>(tmA, tmB, p, sc, static_cast<cudaStream_t>(stream));
+}
+
+int smoe_mxfp8_up_projection_backward_dx_rows(const void* dzq, const void* dz_scale, const void* w1q,
+                                              const void* w1_scale, void* dx, const int* expert_offset,
+                                              const int* x_gather_idx, int H, int I, int E, int TK, int* status,
+                                              void* stream) {
+  if (bad_shape(H, I, E) || TK < 0 || x_gather_idx == nullptr) return SMOE_ERR_SHAPE;
+  if (TK == 0) return SMOE_OK;
+  CUtensorMap tmA, tmB;
+  SMOE_TRY(encode_u8(&tmA, dzq, TK, 2 * I, BM, BK));
+  SMOE_TRY(encode_u8(&tmB, w1q, (uint64_t)E * 2 * I, H, BK, BN_CTA));  // W1[e] (2I, H): rows are k
+  GemmParams p = {};
+  p.E = E; p.N = H; p.K = 2 * I; p.total_rows = TK; p.b_rows_per_expert = 2 * I;
+  p.off = expert_offset; p.gather = x_gather_idx;
+  p.out0 = static_cast<__nv_bfloat16*>(dx); p.ld0 = H;
+  p.status = status;
+  const mx8::ScaleBytes sc = mx_scales(dz_scale, 2 * I, w1_scale, (long long)(2 * I / 128) * (H / 128), 1, H / 128);
+  return launch_mx<false, true, EPI_STORE_ROWS>(tmA, tmB, p, sc, static_cast<cudaStream_t>(stream));
+}
+
 int smoe_mxfp8_down_projection_backward_act(const void* doutq, const void* dout_scale, const void* w2q,
                                             const void* w2_scale, const void* z, const void* scores,
                                             int scores_are_bf16, void* dz, void* y1s, float* ds_partial,

@@ -370,8 +370,9 @@ grouped_gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
       const int ncol0 = tile.n0 + col_half * 128;
       const bool cols_ok = ncol0 < p.N;
       float score = 0.f;
-      if constexpr (EPI == EPI_DSWIGLU || EPI == EPI_SCATTER) {
-        if (row_ok) score = load_score(p.scores, p.scores_are_bf16, p.s_scatter[r]);
+      if constexpr (EPI == EPI_DSWIGLU || EPI == EPI_SCATTER || EPI == EPI_STORE_ROWS) {
+        if (row_ok && (EPI != EPI_STORE_ROWS || p.scores != nullptr))
+          score = load_score(p.scores, p.scores_are_bf16, p.s_scatter[r]);
       }
       if (!mbar_wait(smem_u32(&ss.acc_full), acc_phase, abort_flag)) { ok = false; break; }
       acc_phase ^= 1u;

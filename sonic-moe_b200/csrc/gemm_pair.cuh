@@ -555,8 +555,9 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         const int n0 = tile.n0 + (DUAL == DUAL_N ? sub * BN : 0);
         const bool row_ok = r < tile.row_end;
         float score = 0.f;
-        if constexpr (EPI == EPI_DSWIGLU || EPI == EPI_DACT || EPI == EPI_SCATTER) {
-          if (row_ok) score = load_score(p.scores, p.scores_are_bf16, p.s_scatter[r]);
+        if constexpr (EPI == EPI_DSWIGLU || EPI == EPI_DACT || EPI == EPI_SCATTER || EPI == EPI_STORE_ROWS) {
+          if (row_ok && (EPI != EPI_STORE_ROWS || p.scores != nullptr))
+            score = load_score(p.scores, p.scores_are_bf16, p.s_scatter[r]);
         }
         if (have_acc) {
           if (!mbar_wait(smem_u32(&ss.acc_full[acc]), acc_phase, abort_flag)) { ok = false; break; }

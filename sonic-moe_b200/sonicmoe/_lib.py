@@ -49,6 +49,10 @@ SIGNATURES: dict[str, tuple] = {
     "smoe_ds_reduce": (I, [P, P, P, I, I, I, P]),
     "smoe_up_projection_forward": (I, [P, P, P, P, P, P, I, I, I, I, I, P, P]),
     "smoe_down_projection_forward": (I, [P, P, P, P, I, I, I, I, P, P]),
+    "smoe_down_projection_forward_rows": (I, [P, P, P, P, I, P, P, P, I, I, I, I, P, P]),
+    "smoe_up_projection_backward_dx_rows": (I, [P, P, P, P, P, I, I, I, I, P, P]),
+    "smoe_mxfp8_down_projection_forward_rows": (I, [P, P, P, P, P, P, I, P, P, P, I, I, I, I, P, P]),
+    "smoe_mxfp8_up_projection_backward_dx_rows": (I, [P, P, P, P, P, P, P, I, I, I, I, P, P]),
     "smoe_down_projection_forward_scatter": (I, [P, P, P, P, I, P, P, P, I, I, I, I, I, P, P]),
     "smoe_down_projection_backward_act": (I, [P, P, P, P, I, P, P, P, P, P, P, I, I, I, I, I, P, P]),
     "smoe_ds_partial_columns": (I, [I]),

@@ -89,6 +89,12 @@ class Route:
     K: int                                 # experts per token when token_offset is None
 
 
+def _one_row_per_token(route: "Route", T: int) -> bool:
+    """Every token has exactly one routed row (top-1 routing, or the rows an expert-parallel rank received): the
+    combine and the dX reduction are permutations, which the GEMM epilogues write directly."""
+    return route.token_offset is None and route.K == 1 and route.x_gather_idx.numel() == T
+
+
 def _route_metadata(expert_idx: torch.Tensor, token_idx: torch.Tensor | None, E: int, K: int) -> Route:
     dev = expert_idx.device
     _lib.require_cuda(expert_idx, "expert indices")
@@ -274,7 +280,13 @@ class _RoutedExperts(torch.autograd.Function):
                 x.data_ptr(), w1e.data_ptr(), ptr(z), y1.data_ptr(), route.expert_frequency_offset.data_ptr(),
                 route.x_gather_idx.data_ptr(), T, H, I, E, TK, st.status.data_ptr(), stream), "up_projection_forward")
             o = torch.empty(T, H, dtype=x.dtype, device=dev)
-            if _FUSED_COMBINE:
+            if _one_row_per_token(route, T):
+                check(lib.smoe_down_projection_forward_rows(
+                    y1.data_ptr(), w2e.data_ptr(), o.data_ptr(), scores_flat.data_ptr(),
+                    int(scores_flat.dtype == torch.bfloat16), route.expert_frequency_offset.data_ptr(),
+                    route.x_gather_idx.data_ptr(), route.s_scatter_idx.data_ptr(), H, I, E, TK,
+                    st.status.data_ptr(), stream), "down_projection_forward_rows")
+            elif _FUSED_COMBINE:
                 o_acc = torch.zeros(T, H, dtype=torch.float32, device=dev)
                 check(lib.smoe_down_projection_forward_scatter(
                     y1.data_ptr(), w2e.data_ptr(), o_acc.data_ptr(), scores_flat.data_ptr(),
@@ -333,14 +345,20 @@ class _RoutedExperts(torch.autograd.Function):
             check(lib.smoe_up_projection_weight_grad(
                 x.data_ptr(), dz.data_ptr(), dw1.data_ptr(), off, gat, T, H, I, E, TK, st.status.data_ptr(), stream),
                 "up_projection_weight_grad")
-            dx_expanded = torch.empty(TK, H, dtype=x.dtype, device=dev)
-            check(lib.smoe_up_projection_backward_dx(
-                dz.data_ptr(), w1e.data_ptr(), dx_expanded.data_ptr(), off, H, I, E, TK, st.status.data_ptr(), stream),
-                "up_projection_backward_dx")
             dx = torch.empty(T, H, dtype=x.dtype, device=dev)
-            check(lib.smoe_gather_sum(
-                dx_expanded.data_ptr(), dx.data_ptr(), None, _lib.SMOE_F32, route.s_reverse_scatter_idx.data_ptr(),
-                ptr(route.token_offset), T, H, max(route.K, 1), stream), "gather_sum")
+            if _one_row_per_token(route, T):
+                check(lib.smoe_up_projection_backward_dx_rows(
+                    dz.data_ptr(), w1e.data_ptr(), dx.data_ptr(), off, gat, H, I, E, TK, st.status.data_ptr(), stream),
+                    "up_projection_backward_dx_rows")
+            else:
+                dx_expanded = torch.empty(TK, H, dtype=x.dtype, device=dev)
+                check(lib.smoe_up_projection_backward_dx(
+                    dz.data_ptr(), w1e.data_ptr(), dx_expanded.data_ptr(), off, H, I, E, TK, st.status.data_ptr(),
+                    stream), "up_projection_backward_dx")
+                check(lib.smoe_gather_sum(
+                    dx_expanded.data_ptr(), dx.data_ptr(), None, _lib.SMOE_F32,
+                    route.s_reverse_scatter_idx.data_ptr(), ptr(route.token_offset), T, H, max(route.K, 1), stream),
+                    "gather_sum")
         # gradients in the layout of the (out, in, E) views the caller passed
         return dx, dw1.permute(1, 2, 0), dw2.permute(1, 2, 0), ds, None, None, None
 

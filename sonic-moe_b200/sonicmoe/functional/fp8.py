@@ -103,7 +103,10 @@ class _RoutedExpertsFp8(torch.autograd.Function):
     def forward(ctx, x, w1, w2, scores_flat, route, T: int, inference: bool, fmt: str = None):
         from . import _expert_major
 
+        from . import _one_row_per_token
+
         fmt = _check_format(fmt or _default_scale_format)
+        rows_form = fmt == "ue8m0" and _one_row_per_token(route, T)  # epilogues write o / dx rows directly
         dev = x.device
         x = x.contiguous()
         w1e = _expert_major(w1)
@@ -125,21 +128,29 @@ class _RoutedExpertsFp8(torch.autograd.Function):
                 xq.data_ptr(), xs.data_ptr(), w1q.data_ptr(), w1s.data_ptr(), ptr(z), y1.data_ptr(), off,
                 route.x_gather_idx.data_ptr(), T, H, I, E, TK, st.status.data_ptr(), stream), "fp8_up_projection_forward")
             y1q, y1s = quantize_rows(y1, fmt)
-            y2 = torch.empty(TK, H, dtype=x.dtype, device=dev)
-            check(_entry("down_projection_forward", fmt)(
-                y1q.data_ptr(), y1s.data_ptr(), w2q.data_ptr(), w2s.data_ptr(), y2.data_ptr(), off, H, I, E, TK,
-                st.status.data_ptr(), stream), "fp8_down_projection_forward")
             o = torch.empty(T, H, dtype=x.dtype, device=dev)
-            check(lib.smoe_gather_sum(
-                y2.data_ptr(), o.data_ptr(), scores_flat.data_ptr(), _lib.dtype_code(scores_flat.dtype),
-                route.s_reverse_scatter_idx.data_ptr(), ptr(route.token_offset), T, H, max(route.K, 1), stream),
-                "gather_sum")
+            if rows_form:
+                check(lib.smoe_mxfp8_down_projection_forward_rows(
+                    y1q.data_ptr(), y1s.data_ptr(), w2q.data_ptr(), w2s.data_ptr(), o.data_ptr(),
+                    scores_flat.data_ptr(), int(scores_flat.dtype == torch.bfloat16), off,
+                    route.x_gather_idx.data_ptr(), route.s_scatter_idx.data_ptr(), H, I, E, TK,
+                    st.status.data_ptr(), stream), "mxfp8_down_projection_forward_rows")
+            else:
+                y2 = torch.empty(TK, H, dtype=x.dtype, device=dev)
+                check(_entry("down_projection_forward", fmt)(
+                    y1q.data_ptr(), y1s.data_ptr(), w2q.data_ptr(), w2s.data_ptr(), y2.data_ptr(), off, H, I, E, TK,
+                    st.status.data_ptr(), stream), "fp8_down_projection_forward")
+                check(lib.smoe_gather_sum(
+                    y2.data_ptr(), o.data_ptr(), scores_flat.data_ptr(), _lib.dtype_code(scores_flat.dtype),
+                    route.s_reverse_scatter_idx.data_ptr(), ptr(route.token_offset), T, H, max(route.K, 1), stream),
+                    "gather_sum")
         if not inference:
             # the quantised weights are kept for the backward pass (1 byte per weight) instead of being rebuilt
             ctx.save_for_backward(x, w1e, w2e, z, scores_flat, w1q, w1s, w2q, w2s)
             ctx.route = route
             ctx.dims = (T, H, I, E, TK)
             ctx.fmt = fmt
+            ctx.rows_form = rows_form
         return o
 
     @staticmethod
@@ -177,14 +188,20 @@ class _RoutedExpertsFp8(torch.autograd.Function):
                 x.data_ptr(), dz.data_ptr(), dw1.data_ptr(), off, gat, T, H, I, E, TK, st.status.data_ptr(), stream),
                 "up_projection_weight_grad")
             dzq, dzs = quantize_rows(dz, fmt)
-            dx_expanded = torch.empty(TK, H, dtype=x.dtype, device=dev)
-            check(_entry("up_projection_backward_dx", fmt)(
-                dzq.data_ptr(), dzs.data_ptr(), w1q.data_ptr(), w1s.data_ptr(), dx_expanded.data_ptr(), off, H, I, E,
-                TK, st.status.data_ptr(), stream), "fp8_up_projection_backward_dx")
             dx = torch.empty(T, H, dtype=x.dtype, device=dev)
-            check(lib.smoe_gather_sum(
-                dx_expanded.data_ptr(), dx.data_ptr(), None, _lib.SMOE_F32, route.s_reverse_scatter_idx.data_ptr(),
-                ptr(route.token_offset), T, H, max(route.K, 1), stream), "gather_sum")
+            if ctx.rows_form:
+                check(lib.smoe_mxfp8_up_projection_backward_dx_rows(
+                    dzq.data_ptr(), dzs.data_ptr(), w1q.data_ptr(), w1s.data_ptr(), dx.data_ptr(), off, gat, H, I, E,
+                    TK, st.status.data_ptr(), stream), "mxfp8_up_projection_backward_dx_rows")
+            else:
+                dx_expanded = torch.empty(TK, H, dtype=x.dtype, device=dev)
+                check(_entry("up_projection_backward_dx", fmt)(
+                    dzq.data_ptr(), dzs.data_ptr(), w1q.data_ptr(), w1s.data_ptr(), dx_expanded.data_ptr(), off, H, I,
+                    E, TK, st.status.data_ptr(), stream), "fp8_up_projection_backward_dx")
+                check(lib.smoe_gather_sum(
+                    dx_expanded.data_ptr(), dx.data_ptr(), None, _lib.SMOE_F32,
+                    route.s_reverse_scatter_idx.data_ptr(), ptr(route.token_offset), T, H, max(route.K, 1), stream),
+                    "gather_sum")
         return dx, dw1.permute(1, 2, 0), dw2.permute(1, 2, 0), ds, None, None, None, None
 
 

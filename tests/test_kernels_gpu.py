@@ -182,6 +182,7 @@ SHAPES = [
     (1000, 768, 320, 8, 2, True),    # ragged tiles, N tails, an empty and a hot expert
     (300, 128, 64, 16, 4, True),     # experts far smaller than one tile
     (2048, 1024, 512, 32, 8, False),
+    (1024, 512, 960, 4, 2, True),    # dual-tile units with a partly filled second tile (2I = 1920, I = 960)
 ]
 
 
@@ -351,6 +352,79 @@ def test_kernels_are_deterministic(smoe):
                                        T, H, I, E, T * K, st.data_ptr(), stream)
         outs.append((z, y1))
     assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
+
+
+
+@pytest.mark.parametrize("shape", [(1000, 512, 256, 8, 1, True), (2048, 1024, 512, 16, 1, False)])
+def test_one_row_per_token_forms(smoe, shape):
+    """K = 1: the row-writing epilogues (no y2 / dx_expanded buffer, no gather-and-sum pass) give bit for bit what the
+    store + gather_sum pairs give, in bf16 and with FP8 (ue8m0) operands."""
+    _lib, _ = smoe
+    from sonicmoe.functional import fp8
+
+    lib = _lib.lib
+    T, H, I, E, K, skew = shape
+    inp, f32, scores, route, fwd = _problem(*shape)
+    d = _dev(route)
+    TK = T
+    st = _lib.device_state(torch.device("cuda", 0)).status
+    stream = torch.cuda.current_stream().cuda_stream
+    w1, w2 = inp["w1"].cuda(), inp["w2"].cuda()
+    off, gat, sct, rev = (d["expert_frequency_offset"].data_ptr(), d["x_gather_idx"].data_ptr(),
+                          d["s_scatter_idx"].data_ptr(), d["s_reverse_scatter_idx"].data_ptr())
+    nan = float("nan")
+    g = torch.Generator().manual_seed(3)
+    y1 = torch.randn(TK, I, generator=g).bfloat16().cuda()
+    dz = (torch.randn(TK, 2 * I, generator=g) * 0.1).bfloat16().cuda()
+    for sc in (scores.reshape(-1).cuda(), scores.reshape(-1).bfloat16().cuda()):
+        bf = int(sc.dtype == torch.bfloat16)
+        y2 = torch.empty(TK, H, dtype=torch.bfloat16, device="cuda")
+        o_two = torch.full((T, H), nan, dtype=torch.bfloat16, device="cuda")
+        assert lib.smoe_down_projection_forward(y1.data_ptr(), w2.data_ptr(), y2.data_ptr(), off, H, I, E, TK,
+                                                st.data_ptr(), stream) == 0
+        assert lib.smoe_gather_sum(y2.data_ptr(), o_two.data_ptr(), sc.data_ptr(), _lib.dtype_code(sc.dtype), rev, None,
+                                   T, H, 1, stream) == 0
+        o_one = torch.full((T, H), nan, dtype=torch.bfloat16, device="cuda")
+        assert lib.smoe_down_projection_forward_rows(y1.data_ptr(), w2.data_ptr(), o_one.data_ptr(), sc.data_ptr(), bf,
+                                                     off, gat, sct, H, I, E, TK, st.data_ptr(), stream) == 0
+        assert torch.equal(o_one, o_two)
+    dxe = torch.empty(TK, H, dtype=torch.bfloat16, device="cuda")
+    dx_two = torch.full((T, H), nan, dtype=torch.bfloat16, device="cuda")
+    assert lib.smoe_up_projection_backward_dx(dz.data_ptr(), w1.data_ptr(), dxe.data_ptr(), off, H, I, E, TK,
+                                              st.data_ptr(), stream) == 0
+    assert lib.smoe_gather_sum(dxe.data_ptr(), dx_two.data_ptr(), None, _lib.SMOE_F32, rev, None, T, H, 1, stream) == 0
+    dx_one = torch.full((T, H), nan, dtype=torch.bfloat16, device="cuda")
+    assert lib.smoe_up_projection_backward_dx_rows(dz.data_ptr(), w1.data_ptr(), dx_one.data_ptr(), off, gat, H, I, E,
+                                                   TK, st.data_ptr(), stream) == 0
+    assert torch.equal(dx_one, dx_two)
+
+    # FP8 operands (H, I multiples of 128)
+    if H % 128 == 0 and I % 128 == 0:
+        y1q, y1s = fp8.quantize_rows(y1, "ue8m0")
+        w2q, w2s = fp8.quantize_blocks(w2, "ue8m0")
+        w1q, w1s = fp8.quantize_blocks(w1, "ue8m0")
+        dzq, dzs = fp8.quantize_rows(dz, "ue8m0")
+        sc = scores.reshape(-1).cuda()
+        assert lib.smoe_mxfp8_down_projection_forward(y1q.data_ptr(), y1s.data_ptr(), w2q.data_ptr(), w2s.data_ptr(),
+                                                      y2.data_ptr(), off, H, I, E, TK, st.data_ptr(), stream) == 0
+        assert lib.smoe_gather_sum(y2.data_ptr(), o_two.data_ptr(), sc.data_ptr(), _lib.SMOE_F32, rev, None, T, H, 1,
+                                   stream) == 0
+        o_one.fill_(nan)
+        assert lib.smoe_mxfp8_down_projection_forward_rows(
+            y1q.data_ptr(), y1s.data_ptr(), w2q.data_ptr(), w2s.data_ptr(), o_one.data_ptr(), sc.data_ptr(), 0, off, gat,
+            sct, H, I, E, TK, st.data_ptr(), stream) == 0
+        assert torch.equal(o_one, o_two)
+        assert lib.smoe_mxfp8_up_projection_backward_dx(dzq.data_ptr(), dzs.data_ptr(), w1q.data_ptr(), w1s.data_ptr(),
+                                                        dxe.data_ptr(), off, H, I, E, TK, st.data_ptr(), stream) == 0
+        assert lib.smoe_gather_sum(dxe.data_ptr(), dx_two.data_ptr(), None, _lib.SMOE_F32, rev, None, T, H, 1,
+                                   stream) == 0
+        dx_one.fill_(nan)
+        assert lib.smoe_mxfp8_up_projection_backward_dx_rows(
+            dzq.data_ptr(), dzs.data_ptr(), w1q.data_ptr(), w1s.data_ptr(), dx_one.data_ptr(), off, gat, H, I, E, TK,
+            st.data_ptr(), stream) == 0
+        assert torch.equal(dx_one, dx_two)
+    torch.cuda.synchronize()
+    assert st.item() == 0
 
 
 _DUAL_SNIPPET = """
