@@ -182,7 +182,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         }
       }
       for (int kb = 0; kb < tile.num_kb; ++kb) {
-        if (!mbar_wait_warp(smem_u32(&ss.empty[stage]), phase ^ 1u, abort_flag)) { ok = false; break; }
+        if (!mbar_wait(smem_u32(&ss.empty[stage]), phase ^ 1u, abort_flag)) { ok = false; break; }
         const uint32_t bar = smem_u32(&ss.full[stage]);
         const uint32_t a_dst = smem_u32(sA + stage * A_STAGE_BYTES);
         const uint32_t b_dst = smem_u32(sB + stage * B_STAGE_BYTES);
@@ -259,11 +259,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     Tile tile;
     for (long long t = blockIdx.x; ok && decode_tile<RAGGED_K>(p, ss, t, num_n, tile); t += gridDim.x) {
       if (tile.num_kb == 0) continue;  // empty expert: the epilogue writes zeros without an accumulator
-      if (!mbar_wait_warp(smem_u32(&ss.acc_empty[acc]), acc_phase ^ 1u, abort_flag)) { ok = false; break; }
+      if (!mbar_wait(smem_u32(&ss.acc_empty[acc]), acc_phase ^ 1u, abort_flag)) { ok = false; break; }
       tc_fence_after();
       const uint32_t d_tmem = tmem_base + acc * BN;
       for (int kb = 0; kb < tile.num_kb; ++kb) {
-        if (!mbar_wait_warp(smem_u32(&ss.full[stage]), phase, abort_flag)) { ok = false; break; }
+        if (!mbar_wait(smem_u32(&ss.full[stage]), phase, abort_flag)) { ok = false; break; }
         tc_fence_after();
         if (lane == 0) {
           if constexpr (kLsu) fence_proxy_async_smem();  // stage bytes written by cp.async -> async proxy reads
@@ -311,7 +311,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             src[i] = p.gather_src + static_cast<long long>(idx) * p.gather_ld + c * 8;
           }
           for (int kb = 0; kb < tile.num_kb; ++kb) {
-            if (!mbar_wait_warp(smem_u32(&ss.empty[stage]), phase ^ 1u, abort_flag)) { ok = false; break; }
+            if (!mbar_wait(smem_u32(&ss.empty[stage]), phase ^ 1u, abort_flag)) { ok = false; break; }
             const uint32_t dst = smem_u32(sA + stage * A_STAGE_BYTES) + dst_off;
 #pragma unroll
             for (int i = 0; i < NPASS; ++i) cp_async16(dst + i * (RPP * 128), src[i] + kb * BK, 16);
@@ -347,7 +347,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           load_idx(1, idx1);
           load_idx(2, idx2);
           for (int kb = 0; kb < tile.num_kb; ++kb) {
-            if (!mbar_wait_warp(smem_u32(&ss.empty[stage]), phase ^ 1u, abort_flag)) { ok = false; break; }
+            if (!mbar_wait(smem_u32(&ss.empty[stage]), phase ^ 1u, abort_flag)) { ok = false; break; }
             const uint32_t dst = smem_u32(stage_base + stage * STAGE_BYTES) + chunk * CHUNK_BYTES;
 #pragma unroll
             for (int i = 0; i < PASSES; ++i) {
@@ -384,7 +384,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       const bool row_ok = r < tile.row_end;
       const bool have_acc = tile.num_kb > 0;
       if (have_acc) {
-        if (!mbar_wait_warp(smem_u32(&ss.acc_full[acc]), acc_phase, abort_flag)) { ok = false; break; }
+        if (!mbar_wait(smem_u32(&ss.acc_full[acc]), acc_phase, abort_flag)) { ok = false; break; }
         tc_fence_after();
       }
       float score = 0.f;

@@ -13,12 +13,6 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
 
-__device__ __forceinline__ uint32_t lane_id() {
-  uint32_t l;
-  asm volatile("mov.u32 %0, %%laneid;" : "=r"(l));
-  return l;
-}
-
 __device__ __forceinline__ uint64_t global_timer_ns() {
   uint64_t t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -48,27 +42,10 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
 
-// One probe of the barrier's phase.  The hint lets the hardware park the thread (up to about that many
-// nanoseconds) instead of returning at once, so a waiting thread costs few issue slots and little power.
-#ifndef SMOE_WAIT_HINT
-#define SMOE_WAIT_HINT 0
-#endif
-#ifndef SMOE_WARP_POLL
-#define SMOE_WARP_POLL 0
-#endif
+// One probe of the barrier's phase (returns at once; a suspend-time hint lowered throughput here: the wake-up
+// latency lands on the critical path).
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
-#if SMOE_WAIT_HINT
-  asm volatile(
-      "{\n\t"
-      ".reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t"
-      "}\n"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity), "r"((uint32_t)SMOE_WAIT_HINT)
-      : "memory");
-#else
   asm volatile(
       "{\n\t"
       ".reg .pred p;\n\t"
@@ -78,7 +55,6 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "=r"(ok)
       : "r"(bar), "r"(parity)
       : "memory");
-#endif
   return ok != 0;
 }
 
@@ -103,52 +79,6 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
       }
     }
   }
-}
-
-// Bounded wait for roles that are not on the critical path of the tensor pipe (epilogue and gather warps):
-// every probe lets the hardware park the thread until the phase flips or about a microsecond has passed,
-// so a dozen waiting warps do not keep hammering the barrier word in shared memory.
-__device__ __forceinline__ bool mbar_try_wait_parked(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t"
-      ".reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t"
-      "}\n"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity), "r"(1000u)
-      : "memory");
-  return ok != 0;
-}
-
-__device__ __forceinline__ bool mbar_wait_parked(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-  if (mbar_try_wait_parked(bar, parity)) return true;
-  const uint64_t t0 = global_timer_ns();
-  uint32_t spins = 0;
-  while (true) {
-    if (mbar_try_wait_parked(bar, parity)) return true;
-    if ((++spins & 15u) == 0u) {
-      if (*abort_flag != 0) return false;
-      if (global_timer_ns() - t0 > kWaitLimitNs) {
-        *abort_flag = 1;
-        return false;
-      }
-    }
-  }
-}
-
-// Warp-wide wait: lane 0 watches the barrier, the other 31 lanes sleep at the warp barrier.  Must be
-// called by all 32 lanes.  The result is uniform across the warp.
-__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-#if !SMOE_WARP_POLL
-  return mbar_wait(bar, parity, abort_flag);
-#endif
-  int ok = 1;
-  if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, abort_flag) ? 1 : 0;
-  ok = __shfl_sync(0xffffffffu, ok, 0);
-  __syncwarp();
-  return ok != 0;
 }
 
 // ----------------------------------------------------------------------------------------------
