@@ -3,7 +3,7 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
 
-Workload: BASELINE configs[1] — T=32768 tokens, H=4096, I=1024, E=128 experts, top-K=8, SwiGLU, bf16,
+Workload: benchmark configuration 2 — T=32768 tokens, H=4096, I=1024, E=128 experts, top-K=8, SwiGLU, bf16,
 token-choice softmax top-k routing; weights iid N(0, 0.02), x and upstream gradient iid N(0, 1), seeded,
 synthetic.  One step = one forward + backward of the layer through `sonicmoe.MoE` (all gradients: x,
 router, up and down projections).  FLOP model of the reference benchmark: 18 * T*K * I * H per step
@@ -444,13 +444,13 @@ def run_gpu_arm(args, rank, world, local_rank):
         dist.destroy_process_group()
 
 
-EP_CFG = dict(T=65536, H=2048, I=768, E=64, K=4)  # BASELINE configs[4]: tokens per GPU, Zipf-skewed routing
-EP_FP8_CFG = dict(T=16384, H=7168, I=2048, E=256, K=8)  # BASELINE configs[3]: tokens per GPU, FP8 experts
-ROUNDING_CFG = dict(T=16384, H=4096, I=1024, E=256, K=8)  # BASELINE configs[2]: token rounding to multiples of 128
+EP_CFG = dict(T=65536, H=2048, I=768, E=64, K=4)  # benchmark configuration 5: tokens per GPU, Zipf-skewed routing
+EP_FP8_CFG = dict(T=16384, H=7168, I=2048, E=256, K=8)  # benchmark configuration 4: tokens per GPU, FP8 experts
+ROUNDING_CFG = dict(T=16384, H=4096, I=1024, E=256, K=8)  # benchmark configuration 3: token rounding to multiples of 128
 
 
 def run_rounding_arm(args, local_rank):
-    """Token-rounding routing (BASELINE configs[2]): T=16384, H=4096, I=1024, E=256, K=8; after top-K every expert's
+    """Token-rounding routing (benchmark configuration 3): T=16384, H=4096, I=1024, E=256, K=8; after top-K every expert's
     token count is rounded to the nearest multiple of 128.  As in the reference's benchmark
     (benchmarks/moe-token-rounding.py:355-455) the timed region is the routed layer forward + backward on
     precomputed routing; the router's own time is reported beside it.  FLOPs use the realised pair count."""
@@ -515,9 +515,9 @@ def run_rounding_arm(args, local_rank):
 
 def run_ep_arm(args, rank, world, local_rank, fp8=False):
     """Expert-parallel layer, experts sharded over the ranks, dispatch/combine by NCCL all-to-all.
-    `--workload ep_zipf` (BASELINE configs[4]): T=65536 tokens per GPU, H=2048, I=768, E=64, K=4, router logits
-    biased by 2*log(1/rank_e) with a seeded permutation of expert ranks.  `--workload ep_fp8` (BASELINE
-    configs[3]): T=16384 per GPU, H=7168, I=2048, E=256, K=8, expert GEMMs of forward and activation gradients in
+    `--workload ep_zipf` (benchmark configuration 5): T=65536 tokens per GPU, H=2048, I=768, E=64, K=4, router logits
+    biased by 2*log(1/rank_e) with a seeded permutation of expert ranks.  `--workload ep_fp8` (benchmark
+    configuration 4): T=16384 per GPU, H=7168, I=2048, E=256, K=8, expert GEMMs of forward and activation gradients in
     FP8 E4M3 with 1x128 / 128x128 block scales (weight gradients bf16)."""
     import torch.distributed as dist
 
@@ -595,7 +595,7 @@ def run_ep_arm(args, rank, world, local_rank, fp8=False):
 
 
 def run_fp8_arm(args, local_rank):
-    """The benchmark layer (BASELINE configs[1] shapes) with the expert GEMMs of forward and activation gradients in
+    """The benchmark layer (the default workload's shapes) with the expert GEMMs of forward and activation gradients in
     FP8 E4M3 (1x128 / 128x128 block scales, `--fp8-scales`), weight gradients in bf16: a side workload, not the
     headline line (whose dtype is bf16).  `--kernels-only` times each FP8 GEMM alone on `--tokens` / `--experts`
     (the command the ncu captures of these kernels use)."""

@@ -1,9 +1,9 @@
 """Generate the golden fixtures in this directory by running the REFERENCE's own code on CPU.
 
-Needs the reference checkout (default /root/reference, or $SONICMOE_REFERENCE); it is not needed to run
-the tests, only to regenerate the fixtures:
+Needs a checkout of the reference project, named by $SONICMOE_REFERENCE; it is not needed to run the tests, only to
+regenerate the fixtures:
 
-    python tests/golden/make_golden.py
+    SONICMOE_REFERENCE=<path to the sonic-moe checkout> python tests/golden/make_golden.py
 
 What runs:
   * sonicmoe/moe.py `MoE(...)(x, kernel_backend_moe=KernelBackendMoE.torch)` forward + autograd backward,
@@ -29,7 +29,9 @@ import torch.nn.functional as F
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
-REF = os.environ.get("SONICMOE_REFERENCE", "/root/reference")
+REF = os.environ.get("SONICMOE_REFERENCE")
+if not REF or not os.path.isdir(REF):
+    raise SystemExit("set SONICMOE_REFERENCE to the path of the reference checkout")
 sys.path.insert(0, ROOT)
 sys.dont_write_bytecode = True
 

@@ -39,7 +39,7 @@ def test_layer_forward_backward_matches_reference(name):
 
 
 def test_layer_config1_summaries():
-    """BASELINE config 1 (T2048 H768 I256 E8 K2, fp32): norm, sum and a strided sample of every tensor."""
+    """The CPU-runnable benchmark configuration (T2048 H768 I256 E8 K2, fp32): norm, sum and a strided sample of every tensor."""
     g = golden("layer_cfg1")
     (T, H, I, E, K), inp = _inputs(g["meta"])
     r = orc.moe_layer(inp["x"], inp["router_w"], inp["w1"], inp["w2"], K, dout=inp["dout"])
