@@ -114,6 +114,13 @@ __device__ __forceinline__ uint8_t to_e4m3(float v) {
   return static_cast<uint8_t>(__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3));
 }
 
+// four values -> four E4M3 bytes (two paired conversions), first value in the low byte
+__device__ __forceinline__ uint32_t pack_e4m3x4(float a, float b, float c, float d) {
+  const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
+  const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
+  return lo | (hi << 16);
+}
+
 // Power-of-two scale: the smallest 2^e >= amax / 448, as the UE8M0 byte e + 127 and the exact factor 2^-e.
 __device__ __forceinline__ uint8_t pow2_scale(float amax, float& inv_scale) {
   int e = 0;
@@ -126,55 +133,52 @@ __device__ __forceinline__ uint8_t pow2_scale(float amax, float& inv_scale) {
   return static_cast<uint8_t>(e + 127);
 }
 
-// One warp per (row, 128-column block): power-of-two scale byte at scale[row * ld + block] (ld = blocks per row
-// rounded up to 4; the padding bytes are 2^0), q = x * 2^-e.
-__global__ void __launch_bounds__(256) quantize_rows_pow2_kernel(const __nv_bfloat16* __restrict__ x,
-                                                                 uint8_t* __restrict__ q, uint8_t* __restrict__ scale,
-                                                                 long long rows, int cols, int ld) {
-  const long long w = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (w >= rows * ld) return;
-  const int lane = threadIdx.x & 31;
-  const long long row = w / ld;
-  const int cb = static_cast<int>(w % ld);
-  if (cb >= (cols >> 7)) {
-    if (lane == 0) scale[row * ld + cb] = 0x7F;
-    return;
-  }
-  const uint2 raw = reinterpret_cast<const uint2*>(x + row * cols + cb * 128)[lane];
-  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
-  const float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]);
-  float amax = fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(b.x), fabsf(b.y)));
-#pragma unroll
-  for (int d = 16; d > 0; d >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, d));
-  float inv;
-  const uint8_t byte = pow2_scale(amax, inv);
-  const uint32_t packed = to_e4m3(a.x * inv) | (to_e4m3(a.y * inv) << 8) | (to_e4m3(b.x * inv) << 16) |
-                          (to_e4m3(b.y * inv) << 24);
-  reinterpret_cast<uint32_t*>(q + row * cols + cb * 128)[lane] = packed;
-  if (lane == 0) scale[row * ld + cb] = byte;
-}
-
-// One warp per (row, 128-column block): scale = amax / 448 (1 when the block is all zero), q = x / scale.
+// Row quantiser: one warp per row and group of four 128-column blocks (512 columns): a lane holds 4 values of each
+// block, the four loads are issued together, each block is reduced with shuffles.  POW2: the four scale bytes of the
+// group are one 32-bit word of the padded scale row (ld bytes per row, ld % 4 == 0, padding = 2^0); otherwise fp32
+// scales amax / 448, one per block (ld = blocks per row).
+template <bool POW2>
 __global__ void __launch_bounds__(256) quantize_rows_kernel(const __nv_bfloat16* __restrict__ x,
-                                                            uint8_t* __restrict__ q, float* __restrict__ scale,
-                                                            long long rows, int cols) {
-  const int blocks_per_row = cols >> 7;
+                                                            uint8_t* __restrict__ q, void* __restrict__ scale,
+                                                            long long rows, int cols, int ld) {
+  const int nblk = cols >> 7;
+  const int groups = (nblk + 3) >> 2;
   const long long w = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (w >= rows * blocks_per_row) return;
+  if (w >= rows * groups) return;
   const int lane = threadIdx.x & 31;
-  const long long row = w / blocks_per_row;
-  const int cb = static_cast<int>(w % blocks_per_row);
-  const uint2 raw = reinterpret_cast<const uint2*>(x + row * cols + cb * 128)[lane];
-  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
-  const float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]);
-  float amax = fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(b.x), fabsf(b.y)));
+  const long long row = w / groups;
+  const int g = static_cast<int>(w % groups);
+  const __nv_bfloat16* src = x + row * cols + g * 512;
+  uint2 raw[4];
 #pragma unroll
-  for (int d = 16; d > 0; d >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, d));
-  const float s = amax > 0.f ? amax / 448.f : 1.f;
-  // true division: a reciprocal of a denormal scale would overflow and turn the block's zeros into NaN
-  uint32_t packed = to_e4m3(a.x / s) | (to_e4m3(a.y / s) << 8) | (to_e4m3(b.x / s) << 16) | (to_e4m3(b.y / s) << 24);
-  reinterpret_cast<uint32_t*>(q + row * cols + cb * 128)[lane] = packed;
-  if (lane == 0) scale[row * blocks_per_row + cb] = s;
+  for (int b = 0; b < 4; ++b) {
+    raw[b] = make_uint2(0u, 0u);
+    if (4 * g + b < nblk) raw[b] = reinterpret_cast<const uint2*>(src + b * 128)[lane];
+  }
+  uint32_t word = 0;
+#pragma unroll
+  for (int b = 0; b < 4; ++b) {
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw[b]);
+    const float2 v0 = __bfloat1622float2(h[0]), v1 = __bfloat1622float2(h[1]);
+    float amax = fmaxf(fmaxf(fabsf(v0.x), fabsf(v0.y)), fmaxf(fabsf(v1.x), fabsf(v1.y)));
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, d));
+    const bool live = 4 * g + b < nblk;
+    uint32_t packed;
+    if (POW2) {
+      float inv;
+      const uint32_t byte = pow2_scale(amax, inv);
+      word |= (live ? byte : 0x7Fu) << (8 * b);
+      packed = pack_e4m3x4(v0.x * inv, v0.y * inv, v1.x * inv, v1.y * inv);
+    } else {
+      // true division: a reciprocal of a denormal scale would overflow and turn the block's zeros into NaN
+      const float sc = amax > 0.f ? amax / 448.f : 1.f;
+      packed = pack_e4m3x4(v0.x / sc, v0.y / sc, v1.x / sc, v1.y / sc);
+      if (live && lane == 0) static_cast<float*>(scale)[row * ld + 4 * g + b] = sc;
+    }
+    if (live) reinterpret_cast<uint32_t*>(q + row * cols + g * 512 + b * 128)[lane] = packed;
+  }
+  if (POW2 && lane == 0) reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(scale) + row * ld)[g] = word;
 }
 
 // One CTA per 128 x 128 block of a (batch, rows, cols) tensor; rows need not be a multiple of 128.
@@ -248,9 +252,10 @@ extern "C" {
 int smoe_fp8_quantize_rows(const void* x, void* q, float* scale, long long rows, int cols, void* stream) {
   if (rows < 0 || cols <= 0 || (cols % 128) != 0) return SMOE_ERR_SHAPE;
   if (rows == 0) return SMOE_OK;
-  const long long warps = rows * (cols / 128);
-  quantize_rows_kernel<<<static_cast<unsigned>((warps + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(x), static_cast<uint8_t*>(q), scale, rows, cols);
+  const int nblk = cols / 128;
+  const long long warps = rows * ((nblk + 3) / 4);
+  quantize_rows_kernel<false><<<static_cast<unsigned>((warps + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), static_cast<uint8_t*>(q), scale, rows, cols, nblk);
   return cudaGetLastError() == cudaSuccess ? SMOE_OK : SMOE_ERR_LAUNCH;
 }
 
@@ -348,9 +353,9 @@ int smoe_mxfp8_quantize_rows(const void* x, void* q, void* scale, long long rows
   if (rows == 0) return SMOE_OK;
   if ((reinterpret_cast<uintptr_t>(scale) & 3u) != 0) return SMOE_ERR_ALIGNMENT;
   const int ld = smoe_mxfp8_scale_row_bytes(cols);
-  const long long warps = rows * ld;
-  quantize_rows_pow2_kernel<<<static_cast<unsigned>((warps + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(x), static_cast<uint8_t*>(q), static_cast<uint8_t*>(scale), rows, cols, ld);
+  const long long warps = rows * (ld / 4);
+  quantize_rows_kernel<true><<<static_cast<unsigned>((warps + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), static_cast<uint8_t*>(q), scale, rows, cols, ld);
   return cudaGetLastError() == cudaSuccess ? SMOE_OK : SMOE_ERR_LAUNCH;
 }
 
