@@ -295,6 +295,15 @@ int smoe_mxfp8_down_projection_backward_act(const void* doutq, const void* dout_
                                             const int* expert_offset, const int* x_gather_idx,
                                             const int* s_scatter_idx, int T, int H, int I, int E, int TK, int* status,
                                             void* stream);
+/* As smoe_mxfp8_down_projection_backward_act, and dz also leaves the epilogue quantised: dzq (TK, 2I) E4M3 and
+ * dz_scale (TK, smoe_mxfp8_scale_row_bytes(2I)) UE8M0 bytes, bit-identical to smoe_mxfp8_quantize_rows(dz) (padding
+ * bytes of dz_scale, present when 2I/128 is not a multiple of 4, are left to the caller). */
+int smoe_mxfp8_down_projection_backward_act_q(const void* doutq, const void* dout_scale, const void* w2q,
+                                              const void* w2_scale, const void* z, const void* scores,
+                                              int scores_are_bf16, void* dz, void* y1s, float* ds_partial, void* dzq,
+                                              void* dz_scale, const int* expert_offset, const int* x_gather_idx,
+                                              const int* s_scatter_idx, int T, int H, int I, int E, int TK,
+                                              int* status, void* stream);
 int smoe_mxfp8_up_projection_backward_dx(const void* dzq, const void* dz_scale, const void* w1q, const void* w1_scale,
                                          void* dx_expanded, const int* expert_offset, int H, int I, int E, int TK,
                                          int* status, void* stream);

@@ -56,6 +56,11 @@ struct GemmParams {
   // general epilogues
   const __nv_bfloat16* bias;  // (E, N) added to the accumulator, or nullptr
   int act;                    // Activation code
+  // EPI_DSWIGLU of the hardware-scaled FP8 kernel: dz also leaves the epilogue quantised (E4M3, one UE8M0 scale
+  // byte per row and 128 columns), nullptr = not wanted
+  uint8_t* q_out;             // (total_rows, 2N)
+  uint8_t* q_scale;           // (total_rows, q_scale_ld)
+  long long q_scale_ld;
 };
 
 __device__ __forceinline__ float load_score(const void* scores, int is_bf16, int slot) {
@@ -136,8 +141,51 @@ __device__ __forceinline__ void load_biased(const GemmParams& p, int expert, int
 
 // One 32-column piece of one accumulator row: v[j] = acc[r, n + j] (fp32 bits).  `r` is the grouped row
 // (ragged-M) or the output row inside the expert's matrix (ragged-K); only called for rows that exist.
+// dSwiGLU on 32 accumulator columns (= 64 columns of dz).  acc[., i] = dy1[r, i]; z[r, 2i] = gate, z[r, 2i+1] = up.
+// Writes dz (bf16), y1 * score, accumulates ds.  KEEP: the 32 packed bf16x2 words of dz replace v and amax collects
+// max |dz| over the bf16 values (for a caller that also quantises dz).
+template <bool KEEP>
+__device__ __forceinline__ void dswiglu_chunk(const GemmParams& p, int r, int n, uint32_t (&v)[32], float score,
+                                              float& ds_acc, float& amax) {
+  const uint4* zsrc = reinterpret_cast<const uint4*>(p.z + static_cast<long long>(r) * (2ll * p.N) + 2 * n);
+  __nv_bfloat16* dz_dst = p.out0 + r * p.ld0 + 2 * n;
+  __nv_bfloat16* ys_dst = p.out1 + r * p.ld1 + n;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {  // 8 accumulator columns per step
+    const uint4 za = zsrc[2 * j], zb = zsrc[2 * j + 1];
+    const uint32_t zw[8] = {za.x, za.y, za.z, za.w, zb.x, zb.y, zb.z, zb.w};
+    uint32_t dzw[8];
+    float ys[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const __nv_bfloat162 gu = *reinterpret_cast<const __nv_bfloat162*>(&zw[i]);
+      const float g = __low2float(gu), u = __high2float(gu);
+      const float dy = __uint_as_float(v[8 * j + i]);
+      const float sig = sigmoid_f(g);
+      const float silu = g * sig;
+      const float y1 = silu * u;
+      ds_acc += dy * y1;
+      const float dg = dy * u * (sig * (1.f + g * (1.f - sig))) * score;
+      const float du = dy * silu * score;
+      dzw[i] = pack_bf16(dg, du);
+      ys[i] = y1 * score;
+    }
+    reinterpret_cast<uint4*>(dz_dst)[2 * j] = make_uint4(dzw[0], dzw[1], dzw[2], dzw[3]);
+    reinterpret_cast<uint4*>(dz_dst)[2 * j + 1] = make_uint4(dzw[4], dzw[5], dzw[6], dzw[7]);
+    reinterpret_cast<uint4*>(ys_dst)[j] = make_uint4(pack_bf16(ys[0], ys[1]), pack_bf16(ys[2], ys[3]),
+                                                     pack_bf16(ys[4], ys[5]), pack_bf16(ys[6], ys[7]));
+    if constexpr (KEEP) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        v[8 * j + i] = dzw[i];
+        amax = fmaxf(amax, fmaxf(fabsf(__uint_as_float(dzw[i] << 16)), fabsf(__uint_as_float(dzw[i] & 0xFFFF0000u))));
+      }
+    }
+  }
+}
+
 template <int EPI, bool RAGGED_K>
-__device__ __forceinline__ void epilogue_chunk(const GemmParams& p, int expert, int r, int n, const uint32_t (&v)[32],
+__device__ __forceinline__ void epilogue_chunk(const GemmParams& p, int expert, int r, int n, uint32_t (&v)[32],
                                        float score, float& ds_acc) {
   if constexpr (EPI == EPI_STORE) {
     __nv_bfloat16* dst = p.out0 + (RAGGED_K ? expert * p.out0_expert_stride : 0ll) + r * p.ld0 + n;
@@ -182,35 +230,8 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, int expert, 
       reinterpret_cast<uint4*>(dst1)[j] = w;
     }
   } else if constexpr (EPI == EPI_DSWIGLU) {
-    // acc[., i] = dy1[r, i]; z[r, 2i] = gate, z[r, 2i+1] = up
-    const uint4* zsrc = reinterpret_cast<const uint4*>(p.z + static_cast<long long>(r) * (2ll * p.N) + 2 * n);
-    __nv_bfloat16* dz_dst = p.out0 + r * p.ld0 + 2 * n;
-    __nv_bfloat16* ys_dst = p.out1 + r * p.ld1 + n;
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {  // 8 accumulator columns per step
-      const uint4 za = zsrc[2 * j], zb = zsrc[2 * j + 1];
-      const uint32_t zw[8] = {za.x, za.y, za.z, za.w, zb.x, zb.y, zb.z, zb.w};
-      uint32_t dzw[8];
-      float ys[8];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const __nv_bfloat162 gu = *reinterpret_cast<const __nv_bfloat162*>(&zw[i]);
-        const float g = __low2float(gu), u = __high2float(gu);
-        const float dy = __uint_as_float(v[8 * j + i]);
-        const float sig = sigmoid_f(g);
-        const float silu = g * sig;
-        const float y1 = silu * u;
-        ds_acc += dy * y1;
-        const float dg = dy * u * (sig * (1.f + g * (1.f - sig))) * score;
-        const float du = dy * silu * score;
-        dzw[i] = pack_bf16(dg, du);
-        ys[i] = y1 * score;
-      }
-      reinterpret_cast<uint4*>(dz_dst)[2 * j] = make_uint4(dzw[0], dzw[1], dzw[2], dzw[3]);
-      reinterpret_cast<uint4*>(dz_dst)[2 * j + 1] = make_uint4(dzw[4], dzw[5], dzw[6], dzw[7]);
-      reinterpret_cast<uint4*>(ys_dst)[j] = make_uint4(pack_bf16(ys[0], ys[1]), pack_bf16(ys[2], ys[3]),
-                                                       pack_bf16(ys[4], ys[5]), pack_bf16(ys[6], ys[7]));
-    }
+    float unused = 0.f;
+    dswiglu_chunk<false>(p, r, n, v, score, ds_acc, unused);
   } else if constexpr (EPI == EPI_STORE_BIAS) {
     float f[32];
     load_biased(p, expert, n, v, f);

@@ -121,18 +121,6 @@ __device__ __forceinline__ uint32_t pack_e4m3x4(float a, float b, float c, float
   return lo | (hi << 16);
 }
 
-// Power-of-two scale: the smallest 2^e >= amax / 448, as the UE8M0 byte e + 127 and the exact factor 2^-e.
-__device__ __forceinline__ uint8_t pow2_scale(float amax, float& inv_scale) {
-  int e = 0;
-  if (amax > 0.f) {
-    const float m = frexpf(amax / 448.f, &e);  // amax / 448 = m 2^e, m in [0.5, 1)
-    if (m == 0.5f) --e;
-    e = max(e, -127);
-  }
-  inv_scale = __int_as_float((127 - e) << 23);  // e <= 121 for finite bf16 inputs
-  return static_cast<uint8_t>(e + 127);
-}
-
 // Row quantiser: one warp per row and group of four 128-column blocks (512 columns): a lane holds 4 values of each
 // block, the four loads are issued together, each block is reduced with shuffles.  POW2: the four scale bytes of the
 // group are one 32-bit word of the padded scale row (ld bytes per row, ld % 4 == 0, padding = 2^0); otherwise fp32
@@ -453,7 +441,7 @@ int smoe_mxfp8_up_projection_backward_dx_rows(const void* dzq, const void* dz_sc
   return launch_mx<false, true, EPI_STORE_ROWS>(tmA, tmB, p, sc, static_cast<cudaStream_t>(stream));
 }
 
-int smoe_mxfp8_down_projection_backward_act(const void* doutq, const void* dout_scale, const void* w2q,
+static int mxfp8_dh(void* dzq, void* dz_scale, const void* doutq, const void* dout_scale, const void* w2q,
                                             const void* w2_scale, const void* z, const void* scores,
                                             int scores_are_bf16, void* dz, void* y1s, float* ds_partial,
                                             const int* expert_offset, const int* x_gather_idx,
@@ -472,8 +460,31 @@ int smoe_mxfp8_down_projection_backward_act(const void* doutq, const void* dout_
   p.z = static_cast<const __nv_bfloat16*>(z);
   p.scores = scores; p.scores_are_bf16 = scores_are_bf16; p.ds_partial = ds_partial;
   p.status = status;
+  p.q_out = static_cast<uint8_t*>(dzq); p.q_scale = static_cast<uint8_t*>(dz_scale);
+  p.q_scale_ld = smoe_mxfp8_scale_row_bytes(2 * I);
   const mx8::ScaleBytes sc = mx_scales(dout_scale, H, w2_scale, (long long)(H / 128) * (I / 128), 1, I / 128);
   return launch_mx<true, true, EPI_DSWIGLU>(tmA, tmB, p, sc, static_cast<cudaStream_t>(stream));
+}
+
+int smoe_mxfp8_down_projection_backward_act(const void* doutq, const void* dout_scale, const void* w2q,
+                                            const void* w2_scale, const void* z, const void* scores,
+                                            int scores_are_bf16, void* dz, void* y1s, float* ds_partial,
+                                            const int* expert_offset, const int* x_gather_idx,
+                                            const int* s_scatter_idx, int T, int H, int I, int E, int TK, int* status,
+                                            void* stream) {
+  return mxfp8_dh(nullptr, nullptr, doutq, dout_scale, w2q, w2_scale, z, scores, scores_are_bf16, dz, y1s, ds_partial,
+                  expert_offset, x_gather_idx, s_scatter_idx, T, H, I, E, TK, status, stream);
+}
+
+int smoe_mxfp8_down_projection_backward_act_q(const void* doutq, const void* dout_scale, const void* w2q,
+                                              const void* w2_scale, const void* z, const void* scores,
+                                              int scores_are_bf16, void* dz, void* y1s, float* ds_partial, void* dzq,
+                                              void* dz_scale, const int* expert_offset, const int* x_gather_idx,
+                                              const int* s_scatter_idx, int T, int H, int I, int E, int TK,
+                                              int* status, void* stream) {
+  if (dzq == nullptr || dz_scale == nullptr) return SMOE_ERR_SHAPE;
+  return mxfp8_dh(dzq, dz_scale, doutq, dout_scale, w2q, w2_scale, z, scores, scores_are_bf16, dz, y1s, ds_partial,
+                  expert_offset, x_gather_idx, s_scatter_idx, T, H, I, E, TK, status, stream);
 }
 
 int smoe_mxfp8_up_projection_backward_dx(const void* dzq, const void* dz_scale, const void* w1q, const void* w1_scale,

@@ -94,6 +94,18 @@ __device__ __forceinline__ void umma_e4m3_pair(uint32_t tmem_d, uint64_t desc_a,
       : "memory");
 }
 
+// Power-of-two scale: the smallest 2^e >= amax / 448, as the UE8M0 byte e + 127 and the exact factor 2^-e.
+__device__ __forceinline__ uint8_t pow2_scale(float amax, float& inv_scale) {
+  int e = 0;
+  if (amax > 0.f) {
+    const float m = frexpf(amax / 448.f, &e);  // amax / 448 = m 2^e, m in [0.5, 1)
+    if (m == 0.5f) --e;
+    e = max(e, -127);
+  }
+  inv_scale = __int_as_float((127 - e) << 23);  // e <= 121 for finite bf16 inputs
+  return static_cast<uint8_t>(e + 127);
+}
+
 template <int N>
 __device__ __forceinline__ void reg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
 template <int N>

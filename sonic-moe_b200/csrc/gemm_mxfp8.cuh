@@ -20,6 +20,8 @@
 // Tensor memory: columns 0..255 accumulator, 256.. four sets of scale factors (4 columns A + 8 columns B each).
 // Ragged-M only; every wait is bounded.
 #pragma once
+#include <cuda_fp8.h>
+
 #include "gemm_fp8.cuh"
 
 namespace smoe {
@@ -388,7 +390,45 @@ grouped_gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster_relaxed(map_to_cta(smem_u32(&ss.acc_empty), 0));
       float ds_acc = 0.f;
-      if (row_ok && cols_ok) {
+      bool done = false;
+      if constexpr (EPI == EPI_DSWIGLU) {
+        if (p.q_out != nullptr) {
+          // dz also leaves quantised: this thread's 128 accumulator columns are 256 columns of dz = two scale blocks
+          // of its row, so amax, scale and conversion are thread-local (same arithmetic as the row quantiser on the
+          // bf16 dz: bit-identical bytes)
+          done = true;
+          if (row_ok && cols_ok) {
+            auto quantise_block = [&](uint32_t (&a)[32], uint32_t (&b)[32], int n) {
+              float amax = 0.f;
+              dswiglu_chunk<true>(p, r, n, a, score, ds_acc, amax);
+              dswiglu_chunk<true>(p, r, n + 32, b, score, ds_acc, amax);
+              float inv;
+              const uint8_t byte = fp8::pow2_scale(amax, inv);
+              uint8_t* dst = p.q_out + static_cast<long long>(r) * (2ll * p.N) + 2 * n;
+              auto cvt4 = [&](uint32_t w0, uint32_t w1) {  // two packed bf16 pairs -> four E4M3 bytes
+                const uint32_t lo = __nv_cvt_float2_to_fp8x2(
+                    make_float2(__uint_as_float(w0 << 16) * inv, __uint_as_float(w0 & 0xFFFF0000u) * inv),
+                    __NV_SATFINITE, __NV_E4M3);
+                const uint32_t hi = __nv_cvt_float2_to_fp8x2(
+                    make_float2(__uint_as_float(w1 << 16) * inv, __uint_as_float(w1 & 0xFFFF0000u) * inv),
+                    __NV_SATFINITE, __NV_E4M3);
+                return lo | (hi << 16);
+              };
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                reinterpret_cast<uint4*>(dst)[j] = make_uint4(cvt4(a[8 * j], a[8 * j + 1]), cvt4(a[8 * j + 2], a[8 * j + 3]),
+                                                              cvt4(a[8 * j + 4], a[8 * j + 5]), cvt4(a[8 * j + 6], a[8 * j + 7]));
+                reinterpret_cast<uint4*>(dst + 64)[j] = make_uint4(cvt4(b[8 * j], b[8 * j + 1]), cvt4(b[8 * j + 2], b[8 * j + 3]),
+                                                                   cvt4(b[8 * j + 4], b[8 * j + 5]), cvt4(b[8 * j + 6], b[8 * j + 7]));
+              }
+              p.q_scale[static_cast<long long>(r) * p.q_scale_ld + (2 * n) / 128] = byte;
+            };
+            quantise_block(v0, v1, ncol0);
+            if (ncol0 + 64 < p.N) quantise_block(v2, v3, ncol0 + 64);
+          }
+        }
+      }
+      if (!done && row_ok && cols_ok) {
         epilogue_chunk<EPI, false>(p, tile.e, r, ncol0, v0, score, ds_acc);
         epilogue_chunk<EPI, false>(p, tile.e, r, ncol0 + 32, v1, score, ds_acc);
         epilogue_chunk<EPI, false>(p, tile.e, r, ncol0 + 64, v2, score, ds_acc);

@@ -76,6 +76,7 @@ SIGNATURES: dict[str, tuple] = {
     "smoe_mxfp8_up_projection_forward": (I, [P, P, P, P, P, P, P, P, I, I, I, I, I, P, P]),
     "smoe_mxfp8_down_projection_forward": (I, [P, P, P, P, P, P, I, I, I, I, P, P]),
     "smoe_mxfp8_down_projection_backward_act": (I, [P, P, P, P, P, P, I, P, P, P, P, P, P, I, I, I, I, I, P, P]),
+    "smoe_mxfp8_down_projection_backward_act_q": (I, [P, P, P, P, P, P, I, P, P, P, P, P, P, P, P, I, I, I, I, I, P, P]),
     "smoe_mxfp8_up_projection_backward_dx": (I, [P, P, P, P, P, P, I, I, I, I, P, P]),
 }
 

@@ -171,11 +171,25 @@ class _RoutedExpertsFp8(torch.autograd.Function):
             y1s = torch.empty(TK, I, dtype=x.dtype, device=dev)
             ncols = lib.smoe_ds_partial_columns(I)
             ds_partial = torch.empty(ncols, TK, dtype=torch.float32, device=dev)
-            check(_entry("down_projection_backward_act", fmt)(
-                doutq.data_ptr(), douts.data_ptr(), w2q.data_ptr(), w2s.data_ptr(), z.data_ptr(),
-                scores_flat.data_ptr(), int(scores_flat.dtype == torch.bfloat16), dz.data_ptr(), y1s.data_ptr(),
-                ds_partial.data_ptr(), off, gat, route.s_scatter_idx.data_ptr(), T, H, I, E, TK,
-                st.status.data_ptr(), stream), "fp8_down_projection_backward_act")
+            fused_dz = fmt == "ue8m0"  # the dH epilogue also writes dz quantised (no separate pass over dz)
+            if fused_dz:
+                ld = lib.smoe_mxfp8_scale_row_bytes(2 * I)
+                dzq = torch.empty(TK, 2 * I, dtype=torch.uint8, device=dev)
+                if (2 * I // BLOCK) % 4 == 0:
+                    dzs = torch.empty(TK, ld, dtype=torch.uint8, device=dev)
+                else:  # the kernel does not write the padding bytes of a scale row
+                    dzs = torch.full((TK, ld), 127, dtype=torch.uint8, device=dev)
+                check(lib.smoe_mxfp8_down_projection_backward_act_q(
+                    doutq.data_ptr(), douts.data_ptr(), w2q.data_ptr(), w2s.data_ptr(), z.data_ptr(),
+                    scores_flat.data_ptr(), int(scores_flat.dtype == torch.bfloat16), dz.data_ptr(), y1s.data_ptr(),
+                    ds_partial.data_ptr(), dzq.data_ptr(), dzs.data_ptr(), off, gat, route.s_scatter_idx.data_ptr(),
+                    T, H, I, E, TK, st.status.data_ptr(), stream), "mxfp8_down_projection_backward_act_q")
+            else:
+                check(_entry("down_projection_backward_act", fmt)(
+                    doutq.data_ptr(), douts.data_ptr(), w2q.data_ptr(), w2s.data_ptr(), z.data_ptr(),
+                    scores_flat.data_ptr(), int(scores_flat.dtype == torch.bfloat16), dz.data_ptr(), y1s.data_ptr(),
+                    ds_partial.data_ptr(), off, gat, route.s_scatter_idx.data_ptr(), T, H, I, E, TK,
+                    st.status.data_ptr(), stream), "fp8_down_projection_backward_act")
             ds = torch.empty_like(scores_flat)
             check(lib.smoe_ds_reduce(ds_partial.data_ptr(), route.s_scatter_idx.data_ptr(), ds.data_ptr(),
                                      _lib.dtype_code(ds.dtype), TK, ncols, stream), "ds_reduce")
@@ -187,7 +201,8 @@ class _RoutedExpertsFp8(torch.autograd.Function):
             check(lib.smoe_up_projection_weight_grad(
                 x.data_ptr(), dz.data_ptr(), dw1.data_ptr(), off, gat, T, H, I, E, TK, st.status.data_ptr(), stream),
                 "up_projection_weight_grad")
-            dzq, dzs = quantize_rows(dz, fmt)
+            if not fused_dz:
+                dzq, dzs = quantize_rows(dz, fmt)
             dx = torch.empty(T, H, dtype=x.dtype, device=dev)
             if ctx.rows_form:
                 check(lib.smoe_mxfp8_up_projection_backward_dx_rows(

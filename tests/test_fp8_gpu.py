@@ -168,6 +168,22 @@ def test_fp8_gemms_match_dequantised_products(built_library, shape, fmt):
         dq.data_ptr(), dsc.data_ptr(), w2q.data_ptr(), w2s.data_ptr(), zdev.data_ptr(), sc.data_ptr(), 0,
         dz.data_ptr(), ys.data_ptr(), dsp.data_ptr(), d_off.data_ptr(), d_gat.data_ptr(), d_sct.data_ptr(),
         T, H, I, E, TK, st.data_ptr(), stream) == 0
+    if fmt == "ue8m0":
+        # the variant whose epilogue also quantises dz: same dz / y1s / ds, and bytes + scales identical to the row
+        # quantiser applied to the bf16 dz
+        dz2 = torch.full((TK, 2 * I), nan, dtype=torch.bfloat16, device=dev)
+        ys2 = torch.full((TK, I), nan, dtype=torch.bfloat16, device=dev)
+        dsp2 = torch.zeros(ncols, TK, dtype=torch.float32, device=dev)
+        ld = lib.smoe_mxfp8_scale_row_bytes(2 * I)
+        dzq_f = torch.zeros(TK, 2 * I, dtype=torch.uint8, device=dev)
+        dzs_f = torch.full((TK, ld), 127, dtype=torch.uint8, device=dev)
+        assert lib.smoe_mxfp8_down_projection_backward_act_q(
+            dq.data_ptr(), dsc.data_ptr(), w2q.data_ptr(), w2s.data_ptr(), zdev.data_ptr(), sc.data_ptr(), 0,
+            dz2.data_ptr(), ys2.data_ptr(), dsp2.data_ptr(), dzq_f.data_ptr(), dzs_f.data_ptr(), d_off.data_ptr(),
+            d_gat.data_ptr(), d_sct.data_ptr(), T, H, I, E, TK, st.data_ptr(), stream) == 0
+        assert torch.equal(dz2, dz) and torch.equal(ys2, ys) and torch.equal(dsp2, dsp)
+        dzq_r, dzs_r = fp8.quantize_rows(dz, "ue8m0")
+        assert torch.equal(dzq_f, dzq_r) and torch.equal(dzs_f, dzs_r)
     dy1 = torch.empty(TK, I)
     for e in range(E):
         dy1[off[e]:off[e + 1]] = dd[gat[off[e]:off[e + 1]]] @ w2d[e]
