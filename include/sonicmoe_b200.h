@@ -286,6 +286,14 @@ int smoe_mxfp8_quantize_blocks(const void* w, void* q, void* scale, int batch, i
 int smoe_mxfp8_up_projection_forward(const void* xq, const void* x_scale, const void* w1q, const void* w1_scale,
                                      void* z, void* y1, const int* expert_offset, const int* x_gather_idx, int T,
                                      int H, int I, int E, int TK, int* status, void* stream);
+/* As smoe_mxfp8_up_projection_forward, with y1 leaving the epilogue quantised instead of in bf16: y1q (TK, I) E4M3
+ * and y1_scale (TK, smoe_mxfp8_scale_row_bytes(I)) UE8M0 bytes, bit-identical to smoe_mxfp8_quantize_rows applied to
+ * the bf16 y1 (padding bytes of y1_scale, present when I/128 is not a multiple of 4, are left to the caller).
+ * z == NULL = inference mode. */
+int smoe_mxfp8_up_projection_forward_q(const void* xq, const void* x_scale, const void* w1q, const void* w1_scale,
+                                       void* z, void* y1q, void* y1_scale, const int* expert_offset,
+                                       const int* x_gather_idx, int T, int H, int I, int E, int TK, int* status,
+                                       void* stream);
 int smoe_mxfp8_down_projection_forward(const void* y1q, const void* y1_scale, const void* w2q, const void* w2_scale,
                                        void* y2, const int* expert_offset, int H, int I, int E, int TK, int* status,
                                        void* stream);

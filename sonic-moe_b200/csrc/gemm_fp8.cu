@@ -385,6 +385,26 @@ int smoe_mxfp8_up_projection_forward(const void* xq, const void* x_scale, const 
   return launch_mx<true, false, EPI_SWIGLU>(tmA, tmB, p, sc, static_cast<cudaStream_t>(stream));
 }
 
+int smoe_mxfp8_up_projection_forward_q(const void* xq, const void* x_scale, const void* w1q, const void* w1_scale,
+                                       void* z, void* y1q, void* y1_scale, const int* expert_offset,
+                                       const int* x_gather_idx, int T, int H, int I, int E, int TK, int* status,
+                                       void* stream) {
+  if (bad_shape(H, I, E) || T <= 0 || TK < 0 || y1q == nullptr || y1_scale == nullptr) return SMOE_ERR_SHAPE;
+  if (TK == 0) return SMOE_OK;
+  CUtensorMap tmA, tmB;
+  SMOE_TRY(encode_u8(&tmA, xq, T, H, 1, BK));
+  SMOE_TRY(encode_u8(&tmB, w1q, (uint64_t)E * 2 * I, H, BN_CTA, BK));
+  GemmParams p = {};
+  p.E = E; p.N = 2 * I; p.K = H; p.total_rows = TK; p.gather_rows = T; p.b_rows_per_expert = 2 * I;
+  p.off = expert_offset; p.gather = x_gather_idx;
+  p.out0 = static_cast<__nv_bfloat16*>(z); p.ld0 = 2 * I;
+  p.q_out = static_cast<uint8_t*>(y1q); p.q_scale = static_cast<uint8_t*>(y1_scale);
+  p.q_scale_ld = smoe_mxfp8_scale_row_bytes(I);
+  p.status = status;
+  const mx8::ScaleBytes sc = mx_scales(x_scale, H, w1_scale, (long long)(2 * I / 128) * (H / 128), H / 128, 1);
+  return launch_mx<true, false, EPI_SWIGLU>(tmA, tmB, p, sc, static_cast<cudaStream_t>(stream));
+}
+
 int smoe_mxfp8_down_projection_forward(const void* y1q, const void* y1_scale, const void* w2q, const void* w2_scale,
                                        void* y2, const int* expert_offset, int H, int I, int E, int TK, int* status,
                                        void* stream) {

@@ -68,6 +68,7 @@ struct SharedStorage {
   uint64_t acc_empty;
   uint32_t tmem_base;
   int abort_flag;
+  float row_amax[2][BM];  // EPI_SWIGLU with quantised y1: the two column halves of a row exchange their max |y1|
   int m_tile_prefix[MAX_EXPERTS + 1];
 };
 
@@ -425,6 +426,64 @@ grouped_gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
             };
             quantise_block(v0, v1, ncol0);
             if (ncol0 + 64 < p.N) quantise_block(v2, v3, ncol0 + 64);
+          }
+        }
+      }
+      if constexpr (EPI == EPI_SWIGLU) {
+        if (p.q_out != nullptr) {
+          // y1 leaves quantised.  A scale block of y1 (128 columns) is the tile's whole width of z (256 columns): the
+          // two epilogue warps of a lane quadrant each hold half of it for the same rows and exchange their max |y1|
+          // through shared memory (a 64-thread named barrier per quadrant; both warps walk the same tiles).
+          done = true;
+          uint32_t yw[32];  // 64 y1 values of this row as packed bf16 pairs
+          float amax = 0.f;
+          auto swiglu_keep = [&](uint32_t (&a)[32], int c) {
+            const int n = ncol0 + 32 * c;
+            if (row_ok && cols_ok && p.out0 != nullptr) {
+              __nv_bfloat16* zdst = p.out0 + r * p.ld0 + n;
+#pragma unroll
+              for (int j = 0; j < 4; ++j)
+                reinterpret_cast<uint4*>(zdst)[j] =
+                    make_uint4(pack_bf16(__uint_as_float(a[8 * j]), __uint_as_float(a[8 * j + 1])),
+                               pack_bf16(__uint_as_float(a[8 * j + 2]), __uint_as_float(a[8 * j + 3])),
+                               pack_bf16(__uint_as_float(a[8 * j + 4]), __uint_as_float(a[8 * j + 5])),
+                               pack_bf16(__uint_as_float(a[8 * j + 6]), __uint_as_float(a[8 * j + 7])));
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {  // gate = even column, up = odd column
+              const float g0 = __uint_as_float(a[4 * j]), u0 = __uint_as_float(a[4 * j + 1]);
+              const float g1 = __uint_as_float(a[4 * j + 2]), u1 = __uint_as_float(a[4 * j + 3]);
+              const uint32_t w = pack_bf16(g0 * sigmoid_f(g0) * u0, g1 * sigmoid_f(g1) * u1);
+              yw[8 * c + j] = w;
+              amax = fmaxf(amax, fmaxf(fabsf(__uint_as_float(w << 16)), fabsf(__uint_as_float(w & 0xFFFF0000u))));
+            }
+          };
+          swiglu_keep(v0, 0);
+          swiglu_keep(v1, 1);
+          swiglu_keep(v2, 2);
+          swiglu_keep(v3, 3);
+          ss.row_amax[col_half][row_in_tile] = (row_ok && cols_ok) ? amax : 0.f;
+          asm volatile("bar.sync %0, 64;" ::"r"(1 + quad) : "memory");
+          amax = fmaxf(amax, ss.row_amax[col_half ^ 1][row_in_tile]);
+          asm volatile("bar.sync %0, 64;" ::"r"(1 + quad) : "memory");  // the slots may be rewritten for the next tile
+          if (row_ok && cols_ok) {
+            float inv;
+            const uint8_t byte = fp8::pow2_scale(amax, inv);
+            auto cvt4 = [&](uint32_t w0, uint32_t w1) {
+              const uint32_t lo = __nv_cvt_float2_to_fp8x2(
+                  make_float2(__uint_as_float(w0 << 16) * inv, __uint_as_float(w0 & 0xFFFF0000u) * inv),
+                  __NV_SATFINITE, __NV_E4M3);
+              const uint32_t hi = __nv_cvt_float2_to_fp8x2(
+                  make_float2(__uint_as_float(w1 << 16) * inv, __uint_as_float(w1 & 0xFFFF0000u) * inv),
+                  __NV_SATFINITE, __NV_E4M3);
+              return lo | (hi << 16);
+            };
+            uint8_t* dst = p.q_out + static_cast<long long>(r) * (p.N / 2) + (ncol0 >> 1);
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              reinterpret_cast<uint4*>(dst)[j] = make_uint4(cvt4(yw[8 * j], yw[8 * j + 1]), cvt4(yw[8 * j + 2], yw[8 * j + 3]),
+                                                            cvt4(yw[8 * j + 4], yw[8 * j + 5]), cvt4(yw[8 * j + 6], yw[8 * j + 7]));
+            if (col_half == 0) p.q_scale[static_cast<long long>(r) * p.q_scale_ld + tile.n0 / BN] = byte;
           }
         }
       }

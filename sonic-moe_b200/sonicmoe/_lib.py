@@ -74,6 +74,7 @@ SIGNATURES: dict[str, tuple] = {
     "smoe_mxfp8_quantize_rows": (I, [P, P, P, LL, I, P]),
     "smoe_mxfp8_quantize_blocks": (I, [P, P, P, I, I, I, P]),
     "smoe_mxfp8_up_projection_forward": (I, [P, P, P, P, P, P, P, P, I, I, I, I, I, P, P]),
+    "smoe_mxfp8_up_projection_forward_q": (I, [P, P, P, P, P, P, P, P, P, I, I, I, I, I, P, P]),
     "smoe_mxfp8_down_projection_forward": (I, [P, P, P, P, P, P, I, I, I, I, P, P]),
     "smoe_mxfp8_down_projection_backward_act": (I, [P, P, P, P, P, P, I, P, P, P, P, P, P, I, I, I, I, I, P, P]),
     "smoe_mxfp8_down_projection_backward_act_q": (I, [P, P, P, P, P, P, I, P, P, P, P, P, P, P, P, I, I, I, I, I, P, P]),

@@ -123,11 +123,24 @@ class _RoutedExpertsFp8(torch.autograd.Function):
         with torch.cuda.device(dev):
             stream = stream_ptr(dev)
             z = torch.empty(TK, two_i, dtype=x.dtype, device=dev) if not inference else None
-            y1 = torch.empty(TK, I, dtype=x.dtype, device=dev)
-            check(_entry("up_projection_forward", fmt)(
-                xq.data_ptr(), xs.data_ptr(), w1q.data_ptr(), w1s.data_ptr(), ptr(z), y1.data_ptr(), off,
-                route.x_gather_idx.data_ptr(), T, H, I, E, TK, st.status.data_ptr(), stream), "fp8_up_projection_forward")
-            y1q, y1s = quantize_rows(y1, fmt)
+            if fmt == "ue8m0":  # the up projection's epilogue writes y1 quantised: no bf16 y1, no pass over it
+                y1q = torch.empty(TK, I, dtype=torch.uint8, device=dev)
+                ld = lib.smoe_mxfp8_scale_row_bytes(I)
+                if (I // BLOCK) % 4 == 0:
+                    y1s = torch.empty(TK, ld, dtype=torch.uint8, device=dev)
+                else:  # the kernel does not write the padding bytes of a scale row
+                    y1s = torch.full((TK, ld), 127, dtype=torch.uint8, device=dev)
+                check(lib.smoe_mxfp8_up_projection_forward_q(
+                    xq.data_ptr(), xs.data_ptr(), w1q.data_ptr(), w1s.data_ptr(), ptr(z), y1q.data_ptr(), y1s.data_ptr(),
+                    off, route.x_gather_idx.data_ptr(), T, H, I, E, TK, st.status.data_ptr(), stream),
+                    "mxfp8_up_projection_forward_q")
+            else:
+                y1 = torch.empty(TK, I, dtype=x.dtype, device=dev)
+                check(_entry("up_projection_forward", fmt)(
+                    xq.data_ptr(), xs.data_ptr(), w1q.data_ptr(), w1s.data_ptr(), ptr(z), y1.data_ptr(), off,
+                    route.x_gather_idx.data_ptr(), T, H, I, E, TK, st.status.data_ptr(), stream),
+                    "fp8_up_projection_forward")
+                y1q, y1s = quantize_rows(y1, fmt)
             o = torch.empty(T, H, dtype=x.dtype, device=dev)
             if rows_form:
                 check(lib.smoe_mxfp8_down_projection_forward_rows(

@@ -141,6 +141,20 @@ def test_fp8_gemms_match_dequantised_products(built_library, shape, fmt):
         z_ref[off[e]:off[e + 1]] = xd[gat[off[e]:off[e + 1]]] @ w1d[e].T
     assert rel(z, z_ref) < 1e-2 and rel(y1, orc.swiglu(z_ref)) < 1e-2
 
+    if fmt == "ue8m0":
+        # the variant whose epilogue quantises y1: same z, and bytes + scales identical to the row quantiser applied
+        # to the bf16 y1 of the plain variant
+        z2 = torch.full((TK, 2 * I), nan, dtype=torch.bfloat16, device=dev)
+        ld = lib.smoe_mxfp8_scale_row_bytes(I)
+        y1q_f = torch.zeros(TK, I, dtype=torch.uint8, device=dev)
+        y1s_f = torch.full((TK, ld), 127, dtype=torch.uint8, device=dev)
+        assert lib.smoe_mxfp8_up_projection_forward_q(
+            xq.data_ptr(), xs.data_ptr(), w1q.data_ptr(), w1s.data_ptr(), z2.data_ptr(), y1q_f.data_ptr(),
+            y1s_f.data_ptr(), d_off.data_ptr(), d_gat.data_ptr(), T, H, I, E, TK, st.data_ptr(), stream) == 0
+        assert torch.equal(z2, z)
+        y1q_r, y1s_r = fp8.quantize_rows(y1, "ue8m0")
+        assert torch.equal(y1q_f, y1q_r) and torch.equal(y1s_f, y1s_r)
+
     # down projection
     y1b = orc.swiglu(z_ref).bfloat16().cuda()
     y1q, y1s = fp8.quantize_rows(y1b, fmt)
