@@ -9,8 +9,10 @@ synthetic.  One step = one forward + backward of the layer through `sonicmoe.MoE
 router, up and down projections).  FLOP model of the reference benchmark: 18 * T*K * I * H per step
 (benchmarks/moe-cute.py:231-234, 297-300); router GEMM, softmax and combine are timed but not counted.
 
-With N > 1 every rank runs the whole layer on its own T tokens (replicas, weak scaling, no data-path
-collective); `value` is the sum over ranks.
+With N > 1 the same layer runs expert-parallel: every rank keeps its own T tokens and E/N of the experts, token
+rows travel to the experts' ranks and back with an NCCL all-to-all each way (weak scaling; `value` is the sum over
+ranks).  Before timing, the N > 1 run checks itself: output and gradients of a small slice of every rank's tokens
+against the CPU oracle on the gathered slice (errors in the JSON line).
 
 Prints ONE JSON line (rank 0).  `--impl reference` times the CPU oracle (a port of the reference's
 torch-eager layer) on the host cores on a bounded sample of the same workload.
@@ -133,7 +135,22 @@ def cpu_step(inp, K):
     return time.perf_counter() - t0
 
 
+def time_config1_cpu(reps=3):
+    """The reference's own CPU-runnable case (T2048 H768 I256 E8 K2, fp32, seed 0), whole layer forward+backward."""
+    from oracle import moe_oracle as orc
+
+    c1 = dict(T=2048, H=768, I=256, E=8, K=2)
+    inp = orc.make_inputs(c1["T"], c1["H"], c1["I"], c1["E"], c1["K"], seed=0, dtype=torch.float32)
+    cpu_step(inp, c1["K"])
+    dt = min(cpu_step(inp, c1["K"]) for _ in range(reps))
+    return {"config": c1, "ms_per_step": dt * 1e3,
+            "tflops": flops_per_step(c1["T"], c1["H"], c1["I"], c1["K"]) / dt / 1e12}
+
+
 def run_reference_arm(args, rank, world):
+    """The CPU arm: the oracle port of the reference's torch-eager layer (sonicmoe/moe.py:276-363) on all host
+    threads.  Every step processes CPU_SAMPLE_TOKENS tokens of the benchmark layer (full H, I, E, K): a bounded
+    sample, stated in `config.tokens_per_step` -- the rate, not the step time, is what compares with the GPU arm."""
     if rank != 0:
         return
     cfg = CFG
@@ -148,22 +165,27 @@ def run_reference_arm(args, rank, world):
     value = fl / dt / 1e12
     sample = (f"{CPU_SAMPLE_TOKENS} tokens per step of the same layer (H{cfg['H']} I{cfg['I']} E{cfg['E']} "
               f"K{cfg['K']}), fp32, forward+backward with all gradients")
+    config = dict(workload_config(args.gpus), T=CPU_SAMPLE_TOKENS, tokens_per_step=CPU_SAMPLE_TOKENS,
+                  full_workload_tokens=cfg["T"], l2_policy="n/a (host)")
     line = {
         "impl": "reference", "metric": "moe_fwd_bwd_tflops", "value": value, "unit": "TFLOP/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "tokens_per_s": CPU_SAMPLE_TOKENS / dt,
-        "config": workload_config(args.gpus),
+        "config": config,
         "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
                          "sample": sample},
+        "config1_cpu": time_config1_cpu(),
         "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
 
 
 def workload_config(n_gpus):
+    par = "single" if n_gpus == 1 else f"ep{n_gpus}"
     return {"workload": "moe_layer_fwd_bwd_top8_of_128_T32768_H4096_I1024_swiglu_bf16", **CFG,
-            "routing": "softmax_topk", "parallelism": f"replicas{n_gpus}",
+            "routing": "softmax_topk", "parallelism": par,
+            "tokens": "T per GPU",
             "l2_policy": "inputs larger than L2 (weights 3 GiB, activations > 1 GiB per step)"}
 
 
@@ -513,81 +535,228 @@ def run_rounding_arm(args, local_rank):
     }), flush=True)
 
 
-def run_ep_arm(args, rank, world, local_rank, fp8=False):
+EP_WORKLOADS = {
+    # name: (config, fp8 experts, Zipf logit bias, workload label)
+    "topk": (CFG, False, False, "moe_layer_fwd_bwd_top8_of_128_T32768_H4096_I1024_swiglu_bf16"),
+    "ep_zipf": (EP_CFG, False, True, "moe_layer_fwd_bwd_expert_parallel_zipf_T65536_per_gpu_H2048_I768_E64_K4"),
+    "ep_fp8": (EP_FP8_CFG, True, False, "moe_layer_fwd_bwd_expert_parallel_fp8_T16384_per_gpu_H7168_I2048_E256_K8"),
+}
+EP_PARITY_TOKENS = 2048          # tokens of the gathered batch the in-run parity check uses (all ranks together)
+EP_PARITY_MAX_WEIGHT_BYTES = 16e9  # fp32 copy of all experts the CPU oracle may hold
+
+
+def expert_weights(e, H, I, dev):
+    """Expert e's weights, the same on whichever rank draws them (seeded by the expert's global id)."""
+    g = torch.Generator(device=dev).manual_seed(1000 + e)
+    w1 = (torch.randn(2 * I, H, generator=g, device=dev) * 0.02).bfloat16()
+    w2 = (torch.randn(H, I, generator=g, device=dev) * 0.02).bfloat16()
+    return w1, w2
+
+
+def ep_parity_check(layer, x, dout, router_w, w1, w2, logit_bias, cfg, rank, world, dev):
+    """Expert-parallel forward + backward on a slice of every rank's tokens against the CPU oracle applied to the
+    gathered slice with all E experts (rank 0 draws the other ranks' experts from their seeds).  Returns the relative
+    Frobenius errors (rank 0) -- the run's own evidence that the exchanged result equals the single-device layer."""
+    import torch.distributed as dist
+
+    T, H, I, E, K = (cfg[k] for k in "THIEK")
+    e_local = E // world
+    n = max(128, EP_PARITY_TOKENS // world)
+    xs = x[:n].detach().clone().requires_grad_(True)
+    ds = dout[:n]
+    for p_ in (router_w, w1, w2):
+        p_.grad = None
+    o, logits = layer(xs)
+    o.backward(ds)
+    torch.cuda.synchronize()
+
+    def gathered(t):
+        parts = [torch.empty_like(t) for _ in range(world)]
+        dist.all_gather(parts, t.contiguous())
+        return torch.cat(parts).float().cpu()
+
+    x_all, d_all, o_all, dx_all, lg_all = (gathered(t) for t in (xs.detach(), ds, o.detach(), xs.grad, logits.detach()))
+    drouter = router_w.grad.detach().float().clone()
+    dist.all_reduce(drouter)
+    out = None
+    if rank == 0:
+        from oracle import moe_oracle as orc
+
+        w1_all = torch.empty(E, 2 * I, H)
+        w2_all = torch.empty(E, H, I)
+        for e in range(E):
+            a, b = expert_weights(e, H, I, dev)
+            w1_all[e], w2_all[e] = a.float().cpu(), b.float().cpu()
+        ref = orc.moe_layer(x_all, router_w.detach().float().cpu(), w1_all, w2_all, K, dout=d_all, logits=lg_all)
+
+        def rel(a, b):
+            return ((a.float().cpu() - b).norm() / (b.norm() + 1e-30)).item()
+
+        out = {"tokens": n * world, "o": rel(o_all, ref["o"]), "dx": rel(dx_all, ref["dx"]),
+               "dw1_rank0": rel(w1.grad, ref["dw1"][:e_local]), "dw2_rank0": rel(w2.grad, ref["dw2"][:e_local]),
+               "drouter": rel(drouter, ref["drouter_w"]), "tolerance": 1e-2, "against": "CPU oracle, fp32"}
+        out["ok"] = all(v < out["tolerance"] for k_, v in out.items() if k_ in ("o", "dx", "dw1_rank0", "dw2_rank0",
+                                                                                 "drouter"))
+    for p_ in (router_w, w1, w2):
+        p_.grad = None
+    dist.barrier()
+    return out
+
+
+def run_ep_arm(args, rank, world, local_rank, workload):
     """Expert-parallel layer, experts sharded over the ranks, dispatch/combine by NCCL all-to-all.
-    `--workload ep_zipf` (benchmark configuration 5): T=65536 tokens per GPU, H=2048, I=768, E=64, K=4, router logits
-    biased by 2*log(1/rank_e) with a seeded permutation of expert ranks.  `--workload ep_fp8` (benchmark
+    Default workload with --gpus N > 1: the benchmark layer itself (T=32768 tokens per GPU, E=128 experts, 128/N per
+    rank).  `--workload ep_zipf` (benchmark configuration 5): T=65536 tokens per GPU, H=2048, I=768, E=64, K=4, router
+    logits biased by 2*log(1/rank_e) with a seeded permutation of expert ranks.  `--workload ep_fp8` (benchmark
     configuration 4): T=16384 per GPU, H=7168, I=2048, E=256, K=8, expert GEMMs of forward and activation gradients in
     FP8 E4M3 with 1x128 / 128x128 block scales (weight gradients bf16)."""
     import torch.distributed as dist
 
-    from sonicmoe import _lib
-    from sonicmoe.expert_parallel import Fp8CudaOps, moe_ep_softmax_topk_layer
+    from sonicmoe import _lib, expert_parallel as ep
 
-    cfg = EP_FP8_CFG if fp8 else EP_CFG
-    ops = Fp8CudaOps(args.fp8_scales) if fp8 else None
+    cfg, fp8, zipf, label = EP_WORKLOADS[workload]
+    ops = ep.Fp8CudaOps(args.fp8_scales) if fp8 else None
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
     dist.init_process_group("nccl", device_id=dev)
+    peaks = load_peaks()
     T, H, I, E, K = (cfg[k] for k in "THIEK")
     e_local = E // world
     g = torch.Generator(device=dev).manual_seed(0)
     router_w = (torch.randn(E, H, generator=g, device=dev) * 0.02).bfloat16().requires_grad_(True)
     ranks = torch.randperm(E, generator=g, device=dev) + 1
-    logit_bias = None if fp8 else 2.0 * torch.log(1.0 / ranks.float())
+    logit_bias = 2.0 * torch.log(1.0 / ranks.float()) if zipf else None
+    mine = [expert_weights(rank * e_local + e, H, I, dev) for e in range(e_local)]
+    w1 = torch.stack([m[0] for m in mine]).requires_grad_(True)
+    w2 = torch.stack([m[1] for m in mine]).requires_grad_(True)
+    del mine
     g = torch.Generator(device=dev).manual_seed(1 + rank)
-    w1 = (torch.randn(e_local, 2 * I, H, generator=g, device=dev) * 0.02).bfloat16().requires_grad_(True)
-    w2 = (torch.randn(e_local, H, I, generator=g, device=dev) * 0.02).bfloat16().requires_grad_(True)
-    x = torch.randn(T, H, generator=g, device=dev).bfloat16().requires_grad_(True)
-    dout = torch.randn(T, H, generator=g, device=dev).bfloat16()
-    params = [x, router_w, w1, w2]
+    x_host = torch.randn(T, H, generator=g, device=dev).bfloat16().cpu().pin_memory()
+    dout_host = torch.randn(T, H, generator=g, device=dev).bfloat16().cpu().pin_memory()
+    x = x_host.to(dev).requires_grad_(True)
+    dout = dout_host.to(dev)
+    o_host = torch.empty(T, H, dtype=torch.bfloat16).pin_memory()
+    dx_host = torch.empty(T, H, dtype=torch.bfloat16).pin_memory()
+    params = [router_w, w1, w2]
     stats = {}
 
+    def layer(xs):
+        o, logits, freq = ep.moe_ep_softmax_topk_layer(xs, router_w, w1, w2, K, E, logit_bias=logit_bias, ops=ops)
+        stats["freq"] = freq
+        return o, logits
+
+    parity = None
+    if E * 3.0 * I * H * 4 <= EP_PARITY_MAX_WEIGHT_BYTES:
+        parity = ep_parity_check(layer, x, dout, router_w, w1, w2, logit_bias, cfg, rank, world, dev)
+    elif rank == 0:
+        parity = {"skipped": "an fp32 copy of all experts for the CPU oracle exceeds the host-memory bound of this "
+                             "check; the same path is compared with the oracle in tests/test_expert_parallel.py"}
+
     def step():
+        x.grad = None
         for p_ in params:
             p_.grad = None
-        o, _logits, freq = moe_ep_softmax_topk_layer(x, router_w, w1, w2, K, E, logit_bias=logit_bias, ops=ops)
+        o, _ = layer(x)
         o.backward(dout)
-        stats["freq"] = freq
+
+    def step_e2e():
+        # host buffers in, host buffers out: the copies are part of the step
+        xs = x_host.to(dev, non_blocking=True).requires_grad_(True)
+        ds = dout_host.to(dev, non_blocking=True)
+        for p_ in params:
+            p_.grad = None
+        o, _ = layer(xs)
+        o.backward(ds)
+        o_host.copy_(o.detach(), non_blocking=True)
+        dx_host.copy_(xs.grad, non_blocking=True)
 
     def barrier():
         torch.cuda.synchronize()
         dist.barrier()
         torch.cuda.synchronize()
 
+    def timed(fn, n):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        barrier()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return ms.item() / n
+
     for _ in range(max(args.warmup, 3)):
         step()
     _lib.check_status(dev)
-    barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.steps):
-        step()
-    e1.record()
-    barrier()
-    ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
-    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    launches_before = _lib.launch_count()
+    ms_per_step = timed(step, args.steps)
+    launches = _lib.launch_count() - launches_before
+    clocks = sampler.stop() if rank == 0 else None
+    _lib.check_status(dev)
+
+    # time spent inside the all-to-alls (CUDA events around each one, on the compute stream), max over ranks
+    ep.record_exchanges(True)
+    step()
+    torch.cuda.synchronize()
+    events = ep.record_exchanges(False)
+    a2a = torch.tensor([sum(a.elapsed_time(b) for a, b in events)], device=dev)
+    dist.all_reduce(a2a, op=dist.ReduceOp.MAX)
+
+    step_e2e()
+    e2e_ms = timed(step_e2e, args.steps)
+    _lib.check_status(dev)
+
     freq = stats["freq"].float()
     dist.all_reduce(freq)  # rows per expert over all ranks
-    _lib.check_status(dev)
+    kernels = dominant = None
+    if rank == 0 and not fp8:
+        # the local problem of one rank: all routed rows of T tokens over E/N experts
+        kcfg = dict(cfg, E=e_local, K=min(K, e_local))
+        moe_local = build_layer(kcfg, dev)
+        kernels, dominant, dom_flops = time_kernels(moe_local, x.detach(), dout, kcfg, peaks)
+        del moe_local
     if rank == 0:
-        ms_per_step = ms.item() / args.steps
         total_rows = freq.sum().item()
-        value = 18.0 * total_rows * I * H / (ms_per_step * 1e-3) / 1e12
+        fl = 18.0 * total_rows * I * H
+        value = fl / (ms_per_step * 1e-3) / 1e12
         per_rank_rows = freq.view(world, e_local).sum(1)
         line = {
             "metric": "moe_fwd_bwd_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "fp8_e4m3 (weight gradients bf16)" if fp8 else "bf16", "data": "synthetic",
             "tokens_per_s": world * T / (ms_per_step * 1e-3), "tflops_per_gpu": value / world,
-            "config": {"workload": ("moe_layer_fwd_bwd_expert_parallel_fp8_T16384_per_gpu_H7168_I2048_E256_K8" if fp8 else
-                                    "moe_layer_fwd_bwd_expert_parallel_zipf_T65536_per_gpu_H2048_I768_E64_K4"), **cfg,
-                       "parallelism": f"ep{world}",
-                       "routing": "softmax_topk" if fp8 else "softmax_topk + per-expert logit bias 2*log(1/rank)"},
+            "config": {"workload": label, **cfg, "tokens": "T per GPU", "parallelism": f"ep{world}",
+                       "collective": "NCCL all_to_all_single (token rows once per destination rank, scores, indices)",
+                       "routing": "softmax_topk" + (" + per-expert logit bias 2*log(1/rank)" if zipf else ""),
+                       "l2_policy": "inputs larger than L2"},
             **({"fp8_scale_format": args.fp8_scales} if fp8 else {}),
+            "clocks": clocks,
+            "e2e": {"value": fl / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": 2 * T * H * 2, "d2h_bytes_per_step": 2 * T * H * 2,
+                    "api": "moe_ep_softmax_topk_layer forward + backward; every step copies x and dout from pinned host "
+                           "memory and o and dx back to it (per rank)"},
+            "gpu_launches": launches,
+            "all_to_all_ms_per_step": a2a.item(), "all_to_all_share": a2a.item() / ms_per_step,
             "expert_load_max_over_mean": (freq.max() / freq.mean()).item(),
             "rank_load_max_over_mean": (per_rank_rows.max() / per_rank_rows.mean()).item(),
+            "ep_parity": parity,
+            "comm_nranks_ok": dist.get_world_size() == world,
         }
+        if kernels is not None:
+            achieved = kernels[dominant]["tflops"]
+            line["roofline"] = {"bound": "tensor", "kernel": dominant, "achieved": achieved,
+                                "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                                "frac": round(achieved / peaks["bf16_tflops"], 3),
+                                "peak_source": f"{peaks['source']} cuBLAS bf16 burst", "flops_per_launch": dom_flops,
+                                "traffic": None,
+                                "note": "rank 0's local problem: the routed rows of T tokens over E/N experts"}
+            line["kernels"] = kernels
+        line["cpu_baseline"] = None  # N = 1 only
         print(json.dumps(line), flush=True)
     dist.barrier()
     dist.destroy_process_group()
@@ -728,12 +897,12 @@ def main():
     if args.workload == "fp8":
         run_fp8_arm(args, local_rank)
         return
-    if args.workload in ("ep_zipf", "ep_fp8"):
+    if args.workload in ("ep_zipf", "ep_fp8") or (args.workload == "topk" and world > 1 and not args.kernels_only):
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         os.environ.setdefault("MASTER_PORT", "29541")
         os.environ.setdefault("RANK", "0")
         os.environ.setdefault("WORLD_SIZE", "1")
-        run_ep_arm(args, rank, world, local_rank, fp8=args.workload == "ep_fp8")
+        run_ep_arm(args, rank, world, local_rank, args.workload)
         return
     if args.kernels_only:
         cfg = dict(CFG, T=args.tokens, E=args.experts)

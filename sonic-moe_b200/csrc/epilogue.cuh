@@ -38,8 +38,6 @@ struct GemmParams {
   int b_rows_per_expert;  // ragged-M: rows one expert occupies in B's flattened 2D tensor map
   const int* off;         // (E+1) first grouped row of every expert
   const int* gather;      // (total_rows) source row of every grouped row, or nullptr
-  const __nv_bfloat16* gather_src;  // the tensor the gather reads (LSU-gather variant)
-  long long gather_ld;              // its row pitch in elements
   __nv_bfloat16* out0;
   long long ld0;
   long long out0_expert_stride;  // ragged-K only

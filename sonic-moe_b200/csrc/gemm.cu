@@ -1,14 +1,18 @@
 // Host side of the grouped GEMMs: tensor-map construction and the C-ABI launchers.
-#include "gemm.cuh"
+#include "device_cache.cuh"
 #include "gemm_pair.cuh"
 
-#include <cstdio>
 #include <cstdlib>
 #include <mutex>
 
 #include "../../include/sonicmoe_b200.h"
 
 namespace smoe {
+
+using pair::BK;
+using pair::BM;
+using pair::BN;
+using pair::MAX_EXPERTS;
 
 // cuTensorMapEncodeTiled is fetched through the runtime so that the library links against cudart
 // only and still loads on a machine without a driver.
@@ -52,77 +56,27 @@ static int encode_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t
   const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS && getenv("SMOE_DEBUG") != nullptr) {
-    fprintf(stderr, "smoe: cuTensorMapEncodeTiled failed (CUresult %d): base=%p rows=%llu cols=%llu pitch=%llu box=(%u,%u)\n",
-            static_cast<int>(r), base, (unsigned long long)rows, (unsigned long long)cols,
-            (unsigned long long)pitch_elems, box_rows, box_cols);
-  }
   return r == CUDA_SUCCESS ? SMOE_OK : SMOE_ERR_TENSORMAP;
 }
 
-static int num_sms() {
-  static int sms = 0;
-  if (sms == 0) {
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess) return 0;
-    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) sms = 0;
-  }
-  return sms;
-}
-
-// Gathered operands: the CTA-pair kernels fetch them by TMA tile::gather4 issued from 32 threads spread over the
-// gather warps (SMOE_TMA_GATHER=0: 16-byte cp.async copies instead); the single-CTA kernels use cp.async warps
-// (SMOE_TMA_GATHER=1: gather4 from the producer warp).  SMOE_EPI_WARPS (4|8) and SMOE_GATHER_WARPS (4|8) override
-// the per-kernel warp counts of the single-tile kernels (for tuning runs).
-static int env_int(const char* name, int dflt) {
-  const char* e = getenv(name);
-  return (e != nullptr && e[0] != 0) ? atoi(e) : dflt;
-}
-static bool use_tma_gather() {  // single-CTA kernels: gather4 issued by the producer warp (slow, kept for comparison)
-  static const bool v = env_int("SMOE_TMA_GATHER", 0) == 1;
-  return v;
-}
-static bool use_tma_gather_pair() {  // CTA-pair kernels: gather4 issued by 32 threads spread over the gather warps
-  static const bool v = env_int("SMOE_TMA_GATHER", 1) == 1;
-  return v;
-}
-
-template <bool RAGGED_K, bool A_GATHER, bool A_MN, bool B_GATHER, bool B_MN, int EPI, int EW, int GW>
-static int launch_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, cudaStream_t stream) {
-  auto kernel = grouped_gemm_kernel<RAGGED_K, A_GATHER, A_MN, B_GATHER, B_MN, EPI, EW, GW>;
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_BYTES) != cudaSuccess)
-      return SMOE_ERR_LAUNCH;
-    configured = true;
-  }
-  const int sms = num_sms();
-  if (sms <= 0) return SMOE_ERR_DRIVER;
-  kernel<<<sms, gemm_threads(EW, GW), GEMM_SMEM_BYTES, stream>>>(tmA, tmB, p);
-  return cudaGetLastError() == cudaSuccess ? SMOE_OK : SMOE_ERR_LAUNCH;
-}
-
-// CTA-pair kernels (tcgen05.mma.cta_group::2, 256 x 256 tiles) are the default; SMOE_CTA_PAIR=0 selects
-// the single-CTA kernels (128 x 256 tiles).
-static bool use_cta_pair() {
-  static const bool v = env_int("SMOE_CTA_PAIR", 1) != 0;
-  return v;
-}
-
 // Kernels with a gathered operand work on two tiles per gathered stage (256 x 512 or 512 x 256 units) unless
-// SMOE_DUAL=0.
+// SMOE_DUAL=0 (kept for the test that compares the two forms).
 static bool use_dual_tiles() {
-  static const bool v = env_int("SMOE_DUAL", 1) != 0;
+  static const bool v = [] {
+    const char* e = getenv("SMOE_DUAL");
+    return !(e != nullptr && e[0] == '0');
+  }();
   return v;
 }
 
-template <bool RAGGED_K, bool A_GATHER, bool A_MN, bool B_GATHER, bool B_MN, int EPI, int EW, int GW, bool TG = false,
+template <bool RAGGED_K, bool A_GATHER, bool A_MN, bool B_GATHER, bool B_MN, int EPI, int EW, int GW,
           int DUAL = pair::DUAL_NONE>
-static int launch_pair_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p,
-                               cudaStream_t stream) {
-  auto kernel = pair::grouped_gemm_pair_kernel<RAGGED_K, A_GATHER, A_MN, B_GATHER, B_MN, EPI, EW, GW, TG, DUAL>;
-  static bool configured = false;
-  if (!configured) {
+static int launch_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, cudaStream_t stream) {
+  auto kernel = pair::grouped_gemm_pair_kernel<RAGGED_K, A_GATHER, A_MN, B_GATHER, B_MN, EPI, EW, GW, DUAL>;
+  static PerDeviceFlag configured;
+  const int dev = current_device();
+  if (dev < 0) return SMOE_ERR_DRIVER;
+  if (!configured.test(dev)) {
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, pair::SMEM_BYTES) != cudaSuccess)
       return SMOE_ERR_LAUNCH;
     if (DUAL != pair::DUAL_NONE) {
@@ -131,7 +85,7 @@ static int launch_pair_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, c
       cudaFuncAttributes fa;
       if (cudaFuncGetAttributes(&fa, kernel) != cudaSuccess || fa.numRegs != 128) return SMOE_ERR_LAUNCH;
     }
-    configured = true;
+    configured.set(dev);
   }
   const int sms = num_sms();
   if (sms < 2) return SMOE_ERR_DRIVER;
@@ -150,72 +104,30 @@ static int launch_pair_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, c
   return cudaLaunchKernelEx(&cfg, kernel, tmA, tmB, p) == cudaSuccess ? SMOE_OK : SMOE_ERR_LAUNCH;
 }
 
-// dflt_ew / dflt_gw: the tuned warp counts of the calling entry point.
+// Kernels without a gathered operand: 4 epilogue warps.  Kernels with one: dual tiles (8 epilogue + 4 gather
+// warps) where they pay, else single tiles with 4 epilogue + 8 gather warps.
 template <bool RAGGED_K, bool A_GATHER, bool A_MN, bool B_GATHER, bool B_MN, int EPI>
-static int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, cudaStream_t stream,
-                       int dflt_ew, int dflt_gw) {
-  static const int env_ew = env_int("SMOE_EPI_WARPS", 0);
-  static const int env_gw = env_int("SMOE_GATHER_WARPS", 0);
-  const int ew = (env_ew == 4 || env_ew == 8) ? env_ew : dflt_ew;
-  int gw = (env_gw == 4 || env_gw == 8 || env_gw == 16) ? env_gw : dflt_gw;
+static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, cudaStream_t stream) {
   constexpr bool kGather = A_GATHER || B_GATHER;
-#define SMOE_LAUNCH(EW_, GW_) \
-  return launch_pair_variant<RAGGED_K, A_GATHER, A_MN, B_GATHER, B_MN, EPI, EW_, GW_>(tmA, tmB, p, stream)
   if constexpr (!kGather) {
-    if (ew == 4) SMOE_LAUNCH(4, 0);
-    SMOE_LAUNCH(8, 0);
+    return launch_variant<RAGGED_K, A_GATHER, A_MN, B_GATHER, B_MN, EPI, 4, 0>(tmA, tmB, p, stream);
   } else {
-    if (use_tma_gather_pair()) {
-      // (not for the activation-gradient epilogues: they are long enough that losing the overlap of epilogue and
-      // main loop costs more than the halved gather traffic gains: 2.3-2.5 ms against 2.2 ms)
-      // nor when the doubled dimension is so far from a multiple of 512 that the half-empty last unit wastes more
-      // than an eighth of the MMA work (e.g. N = 768)
-      const int doubled = A_GATHER ? p.N : p.M;
-      const bool fits = ((doubled + 511) / 512 * 512 - doubled) * 8 <= doubled;
-      if (use_dual_tiles() && fits && EPI != EPI_DSWIGLU && EPI != EPI_DACT) {
-        constexpr int kDual = A_GATHER ? pair::DUAL_N : pair::DUAL_M;
-        return launch_pair_variant<RAGGED_K, A_GATHER, A_MN, B_GATHER, B_MN, EPI, 8, 4, true, kDual>(tmA, tmB, p, stream);
-      }
-      if (gw == 8) return launch_pair_variant<RAGGED_K, A_GATHER, A_MN, B_GATHER, B_MN, EPI, 4, 8, true>(tmA, tmB, p, stream);
-      return launch_pair_variant<RAGGED_K, A_GATHER, A_MN, B_GATHER, B_MN, EPI, 4, 4, true>(tmA, tmB, p, stream);
+    // not when the doubled dimension is so far from a multiple of 512 that the half-empty last unit wastes more
+    // than an eighth of the MMA work (e.g. N = 768)
+    const int doubled = A_GATHER ? p.N : p.M;
+    const bool fits = ((doubled + 511) / 512 * 512 - doubled) * 8 <= doubled;
+    // (not yet for the activation-gradient epilogues, whose length leaves the second accumulator held too long)
+    if (use_dual_tiles() && fits && EPI != EPI_DSWIGLU && EPI != EPI_DACT) {
+      constexpr int kDual = A_GATHER ? pair::DUAL_N : pair::DUAL_M;
+      return launch_variant<RAGGED_K, A_GATHER, A_MN, B_GATHER, B_MN, EPI, 8, 4, kDual>(tmA, tmB, p, stream);
     }
-    if constexpr (EPI != EPI_DSWIGLU) {  // 16 gather warps leave too few registers for the dSwiGLU epilogue
-      if (gw == 16) SMOE_LAUNCH(4, 16);
-    }
-    if (gw != 8) gw = 4;
-    if (ew == 4 && gw == 4) SMOE_LAUNCH(4, 4);
-    if (ew == 4 && gw == 8) SMOE_LAUNCH(4, 8);
-    if (ew == 8 && gw == 4) SMOE_LAUNCH(8, 4);
-    SMOE_LAUNCH(8, 8);
+    return launch_variant<RAGGED_K, A_GATHER, A_MN, B_GATHER, B_MN, EPI, 4, 8>(tmA, tmB, p, stream);
   }
-#undef SMOE_LAUNCH
 }
 
-// dflt_ew / dflt_gw: the tuned warp counts of the calling entry point.
-template <bool RAGGED_K, bool A_GATHER, bool A_MN, bool B_GATHER, bool B_MN, int EPI>
-static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, cudaStream_t stream,
-                  int dflt_ew, int dflt_gw) {
-  static const int env_ew = env_int("SMOE_EPI_WARPS", 0);
-  static const int env_gw = env_int("SMOE_GATHER_WARPS", 0);
-  if (use_cta_pair())
-    return launch_pair<RAGGED_K, A_GATHER, A_MN, B_GATHER, B_MN, EPI>(tmA, tmB, p, stream, dflt_ew, dflt_gw);
-  const int ew = (env_ew == 4 || env_ew == 8) ? env_ew : dflt_ew;
-  int gw = (env_gw == 4 || env_gw == 8) ? env_gw : dflt_gw;
-  constexpr bool kGather = A_GATHER || B_GATHER;
-  if (!kGather || use_tma_gather()) gw = 0;
-#define SMOE_LAUNCH(EW_, GW_) \
-  return launch_variant<RAGGED_K, A_GATHER, A_MN, B_GATHER, B_MN, EPI, EW_, GW_>(tmA, tmB, p, stream)
-  if (ew == 4 && gw == 0) SMOE_LAUNCH(4, 0);
-  if (ew == 8 && gw == 0) SMOE_LAUNCH(8, 0);
-  if constexpr (kGather) {
-    if (ew == 4 && gw == 4) SMOE_LAUNCH(4, 4);
-    if (ew == 4 && gw == 8) SMOE_LAUNCH(4, 8);
-    if (ew == 8 && gw == 4) SMOE_LAUNCH(8, 4);
-    if (ew == 8 && gw == 8) SMOE_LAUNCH(8, 8);
-  }
-#undef SMOE_LAUNCH
-  return SMOE_ERR_SHAPE;
-}
+// An empty batch (T == 0, hence TK == 0) is valid: the entry points return at once (weight-gradient entry points
+// after zero-filling their output).  What is refused: negative sizes, or routed rows without any token.
+static bool bad_tokens(int T, int TK) { return T < 0 || TK < 0 || (T == 0 && TK > 0); }
 
 static bool bad_shape(int H, int I, int E) {
   return H <= 0 || I <= 0 || E <= 0 || E > MAX_EXPERTS || (H % 64) != 0 || (I % 64) != 0;
@@ -236,19 +148,18 @@ extern "C" {
 int smoe_up_projection_forward(const void* x, const void* w1, void* z, void* y1, const int* expert_offset,
                                const int* x_gather_idx, int T, int H, int I, int E, int TK, int* status,
                                void* stream) {
-  if (bad_shape(H, I, E) || T <= 0 || TK < 0) return SMOE_ERR_SHAPE;
+  if (bad_shape(H, I, E) || bad_tokens(T, TK)) return SMOE_ERR_SHAPE;
   if (TK == 0) return SMOE_OK;
   CUtensorMap tmA, tmB;
   SMOE_TRY(encode_2d(&tmA, x, T, H, H, 1, BK));                        // gather4 rows of x
-  SMOE_TRY(encode_2d(&tmB, w1, (uint64_t)E * 2 * I, H, H, use_cta_pair() ? pair::BN_CTA : BN, BK));    // W1[e] rows = output features, K-major
+  SMOE_TRY(encode_2d(&tmB, w1, (uint64_t)E * 2 * I, H, H, pair::BN_CTA, BK));    // W1[e] rows = output features, K-major
   GemmParams p = {};
   p.E = E; p.N = 2 * I; p.K = H; p.total_rows = TK; p.gather_rows = T; p.b_rows_per_expert = 2 * I;
   p.off = expert_offset; p.gather = x_gather_idx;
-  p.gather_src = static_cast<const __nv_bfloat16*>(x); p.gather_ld = H;
   p.out0 = static_cast<__nv_bfloat16*>(z); p.ld0 = 2 * I;
   p.out1 = static_cast<__nv_bfloat16*>(y1); p.ld1 = I;
   p.status = status;
-  return launch<false, true, false, false, false, EPI_SWIGLU>(tmA, tmB, p, static_cast<cudaStream_t>(stream), 4, 8);
+  return launch<false, true, false, false, false, EPI_SWIGLU>(tmA, tmB, p, static_cast<cudaStream_t>(stream));
 }
 
 int smoe_down_projection_forward(const void* y1, const void* w2, void* y2, const int* expert_offset, int H, int I,
@@ -257,13 +168,13 @@ int smoe_down_projection_forward(const void* y1, const void* w2, void* y2, const
   if (TK == 0) return SMOE_OK;
   CUtensorMap tmA, tmB;
   SMOE_TRY(encode_2d(&tmA, y1, TK, I, I, BM, BK));
-  SMOE_TRY(encode_2d(&tmB, w2, (uint64_t)E * H, I, I, use_cta_pair() ? pair::BN_CTA : BN, BK));        // W2[e] is (H, I): K-major
+  SMOE_TRY(encode_2d(&tmB, w2, (uint64_t)E * H, I, I, pair::BN_CTA, BK));        // W2[e] is (H, I): K-major
   GemmParams p = {};
   p.E = E; p.N = H; p.K = I; p.total_rows = TK; p.b_rows_per_expert = H;
   p.off = expert_offset;
   p.out0 = static_cast<__nv_bfloat16*>(y2); p.ld0 = H;
   p.status = status;
-  return launch<false, false, false, false, false, EPI_STORE>(tmA, tmB, p, static_cast<cudaStream_t>(stream), 4, 0);
+  return launch<false, false, false, false, false, EPI_STORE>(tmA, tmB, p, static_cast<cudaStream_t>(stream));
 }
 
 int smoe_down_projection_forward_rows(const void* y1, const void* w2, void* o, const void* scores, int scores_are_bf16,
@@ -274,38 +185,38 @@ int smoe_down_projection_forward_rows(const void* y1, const void* w2, void* o, c
   if (x_gather_idx == nullptr || (scores != nullptr && s_scatter_idx == nullptr)) return SMOE_ERR_SHAPE;
   CUtensorMap tmA, tmB;
   SMOE_TRY(encode_2d(&tmA, y1, TK, I, I, BM, BK));
-  SMOE_TRY(encode_2d(&tmB, w2, (uint64_t)E * H, I, I, use_cta_pair() ? pair::BN_CTA : BN, BK));
+  SMOE_TRY(encode_2d(&tmB, w2, (uint64_t)E * H, I, I, pair::BN_CTA, BK));
   GemmParams p = {};
   p.E = E; p.N = H; p.K = I; p.total_rows = TK; p.b_rows_per_expert = H;
   p.off = expert_offset; p.gather = x_gather_idx; p.s_scatter = s_scatter_idx;
   p.scores = scores; p.scores_are_bf16 = scores_are_bf16;
   p.out0 = static_cast<__nv_bfloat16*>(o); p.ld0 = H;
   p.status = status;
-  return launch<false, false, false, false, false, EPI_STORE_ROWS>(tmA, tmB, p, static_cast<cudaStream_t>(stream), 4, 0);
+  return launch<false, false, false, false, false, EPI_STORE_ROWS>(tmA, tmB, p, static_cast<cudaStream_t>(stream));
 }
 
 int smoe_down_projection_forward_scatter(const void* y1, const void* w2, float* o_acc, const void* scores,
                                          int scores_are_bf16, const int* expert_offset, const int* x_gather_idx,
                                          const int* s_scatter_idx, int T, int H, int I, int E, int TK, int* status,
                                          void* stream) {
-  if (bad_shape(H, I, E) || TK < 0 || T <= 0) return SMOE_ERR_SHAPE;
+  if (bad_shape(H, I, E) || bad_tokens(T, TK)) return SMOE_ERR_SHAPE;
   if (TK == 0) return SMOE_OK;
   CUtensorMap tmA, tmB;
   SMOE_TRY(encode_2d(&tmA, y1, TK, I, I, BM, BK));
-  SMOE_TRY(encode_2d(&tmB, w2, (uint64_t)E * H, I, I, use_cta_pair() ? pair::BN_CTA : BN, BK));
+  SMOE_TRY(encode_2d(&tmB, w2, (uint64_t)E * H, I, I, pair::BN_CTA, BK));
   GemmParams p = {};
   p.E = E; p.N = H; p.K = I; p.total_rows = TK; p.gather_rows = T; p.b_rows_per_expert = H;
   p.off = expert_offset; p.gather = x_gather_idx; p.s_scatter = s_scatter_idx;
   p.scores = scores; p.scores_are_bf16 = scores_are_bf16; p.acc_out = o_acc;
   p.status = status;
-  return launch<false, false, false, false, false, EPI_SCATTER>(tmA, tmB, p, static_cast<cudaStream_t>(stream), 4, 0);
+  return launch<false, false, false, false, false, EPI_SCATTER>(tmA, tmB, p, static_cast<cudaStream_t>(stream));
 }
 
 int smoe_down_projection_backward_act(const void* dout, const void* w2, const void* z, const void* scores,
                                       int scores_are_bf16, void* dz, void* y1s, float* ds_partial,
                                       const int* expert_offset, const int* x_gather_idx, const int* s_scatter_idx,
                                       int T, int H, int I, int E, int TK, int* status, void* stream) {
-  if (bad_shape(H, I, E) || TK < 0 || T <= 0) return SMOE_ERR_SHAPE;
+  if (bad_shape(H, I, E) || bad_tokens(T, TK)) return SMOE_ERR_SHAPE;
   if (TK == 0) return SMOE_OK;
   CUtensorMap tmA, tmB;
   SMOE_TRY(encode_2d(&tmA, dout, T, H, H, 1, BK));                     // gather4 rows of dout
@@ -313,23 +224,22 @@ int smoe_down_projection_backward_act(const void* dout, const void* w2, const vo
   GemmParams p = {};
   p.E = E; p.N = I; p.K = H; p.total_rows = TK; p.gather_rows = T; p.b_rows_per_expert = H;
   p.off = expert_offset; p.gather = x_gather_idx; p.s_scatter = s_scatter_idx;
-  p.gather_src = static_cast<const __nv_bfloat16*>(dout); p.gather_ld = H;
   p.out0 = static_cast<__nv_bfloat16*>(dz); p.ld0 = 2 * I;
   p.out1 = static_cast<__nv_bfloat16*>(y1s); p.ld1 = I;
   p.z = static_cast<const __nv_bfloat16*>(z);
   p.scores = scores; p.scores_are_bf16 = scores_are_bf16; p.ds_partial = ds_partial;
   p.status = status;
-  return launch<false, true, false, false, true, EPI_DSWIGLU>(tmA, tmB, p, static_cast<cudaStream_t>(stream), 4, 8);
+  return launch<false, true, false, false, true, EPI_DSWIGLU>(tmA, tmB, p, static_cast<cudaStream_t>(stream));
 }
 
-// ---- general activations and biases (CTA-pair kernels only) ---------------------------------------------
+// ---- general activations and biases ---------------------------------------------
 static bool bad_activation(int a) { return a < ACT_SWIGLU || a > ACT_SILU; }
 
 int smoe_up_projection_forward_act(const void* x, const void* w1, const void* b1, void* z, void* y1,
                                    const int* expert_offset, const int* x_gather_idx, int T, int H, int N1, int E,
                                    int TK, int activation, int* status, void* stream) {
   if (bad_activation(activation) || H <= 0 || (H % 64) != 0 || N1 <= 0 || (N1 % 128) != 0 || E <= 0 ||
-      E > MAX_EXPERTS || T <= 0 || TK < 0)
+      E > MAX_EXPERTS || bad_tokens(T, TK))
     return SMOE_ERR_SHAPE;
   if (TK == 0) return SMOE_OK;
   CUtensorMap tmA, tmB;
@@ -338,12 +248,11 @@ int smoe_up_projection_forward_act(const void* x, const void* w1, const void* b1
   GemmParams p = {};
   p.E = E; p.N = N1; p.K = H; p.total_rows = TK; p.gather_rows = T; p.b_rows_per_expert = N1;
   p.off = expert_offset; p.gather = x_gather_idx;
-  p.gather_src = static_cast<const __nv_bfloat16*>(x); p.gather_ld = H;
   p.out0 = static_cast<__nv_bfloat16*>(z); p.ld0 = N1;
   p.out1 = static_cast<__nv_bfloat16*>(y1); p.ld1 = act_is_gated(activation) ? N1 / 2 : N1;
   p.bias = static_cast<const __nv_bfloat16*>(b1); p.act = activation;
   p.status = status;
-  return launch_pair<false, true, false, false, false, EPI_ACT>(tmA, tmB, p, static_cast<cudaStream_t>(stream), 4, 8);
+  return launch<false, true, false, false, false, EPI_ACT>(tmA, tmB, p, static_cast<cudaStream_t>(stream));
 }
 
 int smoe_down_projection_forward_bias(const void* y1, const void* w2, const void* b2, void* y2,
@@ -360,8 +269,8 @@ int smoe_down_projection_forward_bias(const void* y1, const void* w2, const void
   p.out0 = static_cast<__nv_bfloat16*>(y2); p.ld0 = H;
   p.bias = static_cast<const __nv_bfloat16*>(b2);
   p.status = status;
-  return launch_pair<false, false, false, false, false, EPI_STORE_BIAS>(tmA, tmB, p,
-                                                                        static_cast<cudaStream_t>(stream), 4, 0);
+  return launch<false, false, false, false, false, EPI_STORE_BIAS>(tmA, tmB, p,
+                                                                        static_cast<cudaStream_t>(stream));
 }
 
 int smoe_down_projection_backward_dact(const void* dout, const void* w2, const void* z, const void* scores,
@@ -369,7 +278,7 @@ int smoe_down_projection_backward_dact(const void* dout, const void* w2, const v
                                        const int* expert_offset, const int* x_gather_idx, const int* s_scatter_idx,
                                        int T, int H, int I, int E, int TK, int activation, int* status,
                                        void* stream) {
-  if (bad_activation(activation) || bad_shape(H, I, E) || TK < 0 || T <= 0) return SMOE_ERR_SHAPE;
+  if (bad_activation(activation) || bad_shape(H, I, E) || bad_tokens(T, TK)) return SMOE_ERR_SHAPE;
   if (TK == 0) return SMOE_OK;
   CUtensorMap tmA, tmB;
   SMOE_TRY(encode_2d(&tmA, dout, T, H, H, 1, BK));
@@ -378,14 +287,13 @@ int smoe_down_projection_backward_dact(const void* dout, const void* w2, const v
   GemmParams p = {};
   p.E = E; p.N = I; p.K = H; p.total_rows = TK; p.gather_rows = T; p.b_rows_per_expert = H;
   p.off = expert_offset; p.gather = x_gather_idx; p.s_scatter = s_scatter_idx;
-  p.gather_src = static_cast<const __nv_bfloat16*>(dout); p.gather_ld = H;
   p.out0 = static_cast<__nv_bfloat16*>(dz); p.ld0 = n1;
   p.out1 = static_cast<__nv_bfloat16*>(y1s); p.ld1 = I;
   p.z = static_cast<const __nv_bfloat16*>(z);
   p.scores = scores; p.scores_are_bf16 = scores_are_bf16; p.ds_partial = ds_partial;
   p.act = activation;
   p.status = status;
-  return launch_pair<false, true, false, false, true, EPI_DACT>(tmA, tmB, p, static_cast<cudaStream_t>(stream), 4, 8);
+  return launch<false, true, false, false, true, EPI_DACT>(tmA, tmB, p, static_cast<cudaStream_t>(stream));
 }
 
 int smoe_ds_partial_columns(int I) { return 2 * ((I + BN - 1) / BN); }
@@ -402,7 +310,7 @@ int smoe_up_projection_backward_dx(const void* dz, const void* w1, void* dx_expa
   p.off = expert_offset;
   p.out0 = static_cast<__nv_bfloat16*>(dx_expanded); p.ld0 = H;
   p.status = status;
-  return launch<false, false, false, false, true, EPI_STORE>(tmA, tmB, p, static_cast<cudaStream_t>(stream), 4, 0);
+  return launch<false, false, false, false, true, EPI_STORE>(tmA, tmB, p, static_cast<cudaStream_t>(stream));
 }
 
 int smoe_up_projection_backward_dx_rows(const void* dz, const void* w1, void* dx, const int* expert_offset,
@@ -418,13 +326,13 @@ int smoe_up_projection_backward_dx_rows(const void* dz, const void* w1, void* dx
   p.off = expert_offset; p.gather = x_gather_idx;
   p.out0 = static_cast<__nv_bfloat16*>(dx); p.ld0 = H;
   p.status = status;
-  return launch<false, false, false, false, true, EPI_STORE_ROWS>(tmA, tmB, p, static_cast<cudaStream_t>(stream), 4, 0);
+  return launch<false, false, false, false, true, EPI_STORE_ROWS>(tmA, tmB, p, static_cast<cudaStream_t>(stream));
 }
 
 int smoe_down_projection_weight_grad(const void* dout, const void* y1s, void* dw2, const int* expert_offset,
                                      const int* x_gather_idx, int T, int H, int I, int E, int TK, int* status,
                                      void* stream) {
-  if (bad_shape(H, I, E) || TK < 0 || T <= 0) return SMOE_ERR_SHAPE;
+  if (bad_shape(H, I, E) || bad_tokens(T, TK)) return SMOE_ERR_SHAPE;
   if (TK == 0) {
     return cudaMemsetAsync(dw2, 0, (size_t)E * H * I * 2, static_cast<cudaStream_t>(stream)) == cudaSuccess
                ? SMOE_OK : SMOE_ERR_LAUNCH;
@@ -435,16 +343,15 @@ int smoe_down_projection_weight_grad(const void* dout, const void* y1s, void* dw
   GemmParams p = {};
   p.E = E; p.M = H; p.N = I; p.total_rows = TK; p.gather_rows = T;
   p.off = expert_offset; p.gather = x_gather_idx;
-  p.gather_src = static_cast<const __nv_bfloat16*>(dout); p.gather_ld = H;
   p.out0 = static_cast<__nv_bfloat16*>(dw2); p.ld0 = I; p.out0_expert_stride = (long long)H * I;
   p.status = status;
-  return launch<true, true, true, false, true, EPI_STORE>(tmA, tmB, p, static_cast<cudaStream_t>(stream), 8, 8);
+  return launch<true, true, true, false, true, EPI_STORE>(tmA, tmB, p, static_cast<cudaStream_t>(stream));
 }
 
 int smoe_up_projection_weight_grad(const void* x, const void* dz, void* dw1, const int* expert_offset,
                                    const int* x_gather_idx, int T, int H, int I, int E, int TK, int* status,
                                    void* stream) {
-  if (bad_shape(H, I, E) || TK < 0 || T <= 0) return SMOE_ERR_SHAPE;
+  if (bad_shape(H, I, E) || bad_tokens(T, TK)) return SMOE_ERR_SHAPE;
   if (TK == 0) {
     return cudaMemsetAsync(dw1, 0, (size_t)E * 2 * I * H * 2, static_cast<cudaStream_t>(stream)) == cudaSuccess
                ? SMOE_OK : SMOE_ERR_LAUNCH;
@@ -455,10 +362,9 @@ int smoe_up_projection_weight_grad(const void* x, const void* dz, void* dw1, con
   GemmParams p = {};
   p.E = E; p.M = 2 * I; p.N = H; p.total_rows = TK; p.gather_rows = T;
   p.off = expert_offset; p.gather = x_gather_idx;
-  p.gather_src = static_cast<const __nv_bfloat16*>(x); p.gather_ld = H;
   p.out0 = static_cast<__nv_bfloat16*>(dw1); p.ld0 = H; p.out0_expert_stride = (long long)2 * I * H;
   p.status = status;
-  return launch<true, false, true, true, true, EPI_STORE>(tmA, tmB, p, static_cast<cudaStream_t>(stream), 8, 8);
+  return launch<true, false, true, true, true, EPI_STORE>(tmA, tmB, p, static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

@@ -1,5 +1,6 @@
 // FP8 (E4M3) entry points: quantisation kernels and the launchers of the FP8 grouped GEMMs, for fp32 block
 // scales (amax / 448, applied in software) and for power-of-two UE8M0 block scales (applied by the tensor cores).
+#include "device_cache.cuh"
 #include "gemm_fp8.cuh"
 #include "gemm_mxfp8.cuh"
 
@@ -52,26 +53,18 @@ static int encode_u8(CUtensorMap* map, const void* base, uint64_t rows, uint64_t
   return r == CUDA_SUCCESS ? SMOE_OK : SMOE_ERR_TENSORMAP;
 }
 
-static int num_sms() {
-  static int sms = 0;
-  if (sms == 0) {
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess) return 0;
-    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) sms = 0;
-  }
-  return sms;
-}
-
 template <class Kernel, class ScaleArgs>
-static int launch_kernel(Kernel kernel, bool& configured, int smem_bytes, const CUtensorMap& tmA,
+static int launch_kernel(Kernel kernel, PerDeviceFlag& configured, int smem_bytes, const CUtensorMap& tmA,
                          const CUtensorMap& tmB, const GemmParams& p, const ScaleArgs& sc, cudaStream_t stream) {
-  if (!configured) {
+  const int dev = current_device();
+  if (dev < 0) return SMOE_ERR_DRIVER;
+  if (!configured.test(dev)) {
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) != cudaSuccess)
       return SMOE_ERR_LAUNCH;
     // setmaxnreg 56 / 200 in these kernels balances only around 128 registers per thread at launch
     cudaFuncAttributes fa;
     if (cudaFuncGetAttributes(&fa, kernel) != cudaSuccess || fa.numRegs != 128) return SMOE_ERR_LAUNCH;
-    configured = true;
+    configured.set(dev);
   }
   const int sms = num_sms();
   if (sms < 2) return SMOE_ERR_DRIVER;
@@ -93,17 +86,21 @@ static int launch_kernel(Kernel kernel, bool& configured, int smem_bytes, const 
 template <bool A_GATHER, bool B_MN, int EPI>
 static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, const Scales& sc,
                   cudaStream_t stream) {
-  static bool configured = false;
+  static PerDeviceFlag configured;
   return launch_kernel(grouped_gemm_fp8_kernel<A_GATHER, B_MN, EPI>, configured, SMEM_BYTES, tmA, tmB, p, sc, stream);
 }
 
 template <bool A_GATHER, bool B_MN, int EPI>
 static int launch_mx(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, const mx8::ScaleBytes& sc,
                      cudaStream_t stream) {
-  static bool configured = false;
+  static PerDeviceFlag configured;
   return launch_kernel(mx8::grouped_gemm_mxfp8_kernel<A_GATHER, B_MN, EPI>, configured, mx8::SMEM_BYTES, tmA, tmB, p,
                        sc, stream);
 }
+
+// An empty batch (T == 0, hence TK == 0) is valid: the entry points return at once (weight-gradient entry points
+// after zero-filling their output).  What is refused: negative sizes, or routed rows without any token.
+static bool bad_tokens(int T, int TK) { return T < 0 || TK < 0 || (T == 0 && TK > 0); }
 
 static bool bad_shape(int H, int I, int E) {
   return H <= 0 || I <= 0 || E <= 0 || E > MAX_EXPERTS || (H % 128) != 0 || (I % 128) != 0;
@@ -258,7 +255,7 @@ int smoe_fp8_quantize_blocks(const void* w, void* q, float* scale, int batch, in
 int smoe_fp8_up_projection_forward(const void* xq, const float* x_scale, const void* w1q, const float* w1_scale,
                                    void* z, void* y1, const int* expert_offset, const int* x_gather_idx, int T, int H,
                                    int I, int E, int TK, int* status, void* stream) {
-  if (bad_shape(H, I, E) || T <= 0 || TK < 0) return SMOE_ERR_SHAPE;
+  if (bad_shape(H, I, E) || bad_tokens(T, TK)) return SMOE_ERR_SHAPE;
   if (TK == 0) return SMOE_OK;
   CUtensorMap tmA, tmB;
   SMOE_TRY(encode_u8(&tmA, xq, T, H, 1, BK));
@@ -296,7 +293,7 @@ int smoe_fp8_down_projection_backward_act(const void* doutq, const float* dout_s
                                           const int* expert_offset, const int* x_gather_idx,
                                           const int* s_scatter_idx, int T, int H, int I, int E, int TK, int* status,
                                           void* stream) {
-  if (bad_shape(H, I, E) || TK < 0 || T <= 0) return SMOE_ERR_SHAPE;
+  if (bad_shape(H, I, E) || bad_tokens(T, TK)) return SMOE_ERR_SHAPE;
   if (TK == 0) return SMOE_OK;
   CUtensorMap tmA, tmB;
   SMOE_TRY(encode_u8(&tmA, doutq, T, H, 1, BK));
@@ -370,7 +367,7 @@ static mx8::ScaleBytes mx_scales(const void* a, int a_cols, const void* b, long 
 int smoe_mxfp8_up_projection_forward(const void* xq, const void* x_scale, const void* w1q, const void* w1_scale,
                                      void* z, void* y1, const int* expert_offset, const int* x_gather_idx, int T,
                                      int H, int I, int E, int TK, int* status, void* stream) {
-  if (bad_shape(H, I, E) || T <= 0 || TK < 0) return SMOE_ERR_SHAPE;
+  if (bad_shape(H, I, E) || bad_tokens(T, TK)) return SMOE_ERR_SHAPE;
   if (TK == 0) return SMOE_OK;
   CUtensorMap tmA, tmB;
   SMOE_TRY(encode_u8(&tmA, xq, T, H, 1, BK));
@@ -389,7 +386,7 @@ int smoe_mxfp8_up_projection_forward_q(const void* xq, const void* x_scale, cons
                                        void* z, void* y1q, void* y1_scale, const int* expert_offset,
                                        const int* x_gather_idx, int T, int H, int I, int E, int TK, int* status,
                                        void* stream) {
-  if (bad_shape(H, I, E) || T <= 0 || TK < 0 || y1q == nullptr || y1_scale == nullptr) return SMOE_ERR_SHAPE;
+  if (bad_shape(H, I, E) || bad_tokens(T, TK) || y1q == nullptr || y1_scale == nullptr) return SMOE_ERR_SHAPE;
   if (TK == 0) return SMOE_OK;
   CUtensorMap tmA, tmB;
   SMOE_TRY(encode_u8(&tmA, xq, T, H, 1, BK));
@@ -467,7 +464,7 @@ static int mxfp8_dh(void* dzq, void* dz_scale, const void* doutq, const void* do
                                             const int* expert_offset, const int* x_gather_idx,
                                             const int* s_scatter_idx, int T, int H, int I, int E, int TK, int* status,
                                             void* stream) {
-  if (bad_shape(H, I, E) || TK < 0 || T <= 0) return SMOE_ERR_SHAPE;
+  if (bad_shape(H, I, E) || bad_tokens(T, TK)) return SMOE_ERR_SHAPE;
   if (TK == 0) return SMOE_OK;
   CUtensorMap tmA, tmB;
   SMOE_TRY(encode_u8(&tmA, doutq, T, H, 1, BK));

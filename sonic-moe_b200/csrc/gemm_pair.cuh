@@ -13,15 +13,15 @@
 // Roles per CTA (warp index):
 //   0        TMA producer for the operands that are not gathered (both CTAs; completion bytes are counted
 //            on the leader CTA's "full" barrier)
-//   1        leader CTA: MMA issuer.  other CTA: relay that forwards "my gathered rows have landed" to the
-//            leader's full barrier (kernels with a gathered operand), otherwise idle
+//   1        leader CTA: MMA issuer.  other CTA: idle
 //   2..      EW epilogue warps (4 or 8)
-//   2+EW..   GW gather warps (0, 4 or 8): 16-byte cp.async row gathers into the swizzled stage
+//   2+EW..   GW gather warps (0, 4 or 8): the routed rows of the gathered operand by TMA tile::gather4, issued
+//            from 32 threads spread over these warps (gather4 operations issued by one warp are serialised)
 //
-// Barriers.  full[s]: leader only; arrivals = 1 (leader's expect_tx) + 1 (relay, gathered kernels), tx =
-// TMA bytes of both CTAs.  gfull[s]: per CTA, one arrival per gather thread (cp.async completion).
-// empty[s], acc_full[a]: per CTA, signalled by the leader's multicast tcgen05.commit.  acc_empty[a]:
-// leader only, one arrival per epilogue warp of both CTAs.  Every wait is bounded (ptx.cuh).
+// Barriers.  full[s]: leader only; one arrival (the leader's expect_tx), tx = TMA bytes of both CTAs,
+// gathered rows included.  empty[s], acc_full[a]: per CTA, signalled by the leader's multicast
+// tcgen05.commit.  acc_empty[a]: leader only, one arrival per epilogue warp of both CTAs.  Every wait is
+// bounded (ptx.cuh).
 #pragma once
 #include "epilogue.cuh"
 #include "ptx.cuh"
@@ -48,7 +48,6 @@ __host__ __device__ constexpr int threads(int epi_warps, int gather_warps, bool 
 
 struct SharedStorage {
   uint64_t full[STAGES];
-  uint64_t gfull[STAGES];
   uint64_t empty[STAGES];
   uint64_t acc_full[2];
   uint64_t acc_empty[2];
@@ -139,9 +138,7 @@ __device__ __forceinline__ int unit_num_kb(const GemmParams& p, long long t, lon
   }
 }
 
-// TG: the gather warps fetch rows with TMA tile::gather4 (32 issuing threads spread over the gather warps)
-// instead of 16-byte cp.async copies; completion then goes straight to the leader's full barrier.
-template <bool RAGGED_K, bool A_GATHER, bool A_MN, bool B_GATHER, bool B_MN, int EPI, int EW, int GW, bool TG = false,
+template <bool RAGGED_K, bool A_GATHER, bool A_MN, bool B_GATHER, bool B_MN, int EPI, int EW, int GW,
           int DUAL = DUAL_NONE>
 __global__ void __launch_bounds__(threads(EW, GW, DUAL != 0), 1)
 grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -177,15 +174,12 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
   constexpr int FIRST_EPI_WARP = DUAL != DUAL_NONE ? 4 : 2;
   constexpr int FIRST_GATHER_WARP = FIRST_EPI_WARP + EW;
   static_assert(DUAL == DUAL_NONE || (EW == 8 && GW == 4), "dual tiles: 8 epilogue warps, 4 gather warps (512 threads)");
-  constexpr bool kLsuGather = kGather && !TG;  // gathered bytes arrive through cp.async (not counted as tx bytes)
-  constexpr uint32_t kTmaBytesPerCta =
-      (A_GATHER && !TG ? 0 : A_STAGE_BYTES) + (B_GATHER && !TG ? 0 : B_STAGE_BYTES) + X_STAGE_BYTES;
+  constexpr uint32_t kTmaBytesPerCta = A_STAGE_BYTES + B_STAGE_BYTES + X_STAGE_BYTES;  // gathered rows included
 
   // ---- set-up -------------------------------------------------------------------------------
   if (threadIdx.x == 0) {
     for (int s = 0; s < NSTAGES; ++s) {
-      mbar_init(smem_u32(&ss.full[s]), 1 + (kLsuGather ? 1 : 0));
-      mbar_init(smem_u32(&ss.gfull[s]), kLsuGather ? GATHER_THREADS : 1);
+      mbar_init(smem_u32(&ss.full[s]), 1);
       mbar_init(smem_u32(&ss.empty[s]), 1);
     }
     for (int a = 0; a < 2; ++a) {
@@ -316,14 +310,10 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         const uint32_t d_tmem = tmem_base + (DUAL == DUAL_NONE ? acc * BN : 0);
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(smem_u32(&ss.full[stage]), phase, abort_flag)) { ok = false; break; }
-          if constexpr (kLsuGather) {
-            if (!mbar_wait(smem_u32(&ss.gfull[stage]), phase, abort_flag)) { ok = false; break; }
-          }
           tc_fence_after();
           const uint64_t a_desc = make_smem_desc(smem_u32(sA + stage * A_STAGE_BYTES), a_lbo, 1024);
           const uint64_t b_desc = make_smem_desc(smem_u32(sB + stage * B_STAGE_BYTES), b_lbo, 1024);
           if (lane == 0) {
-            if constexpr (kLsuGather) fence_proxy_async_smem();
 #pragma unroll
             for (int k4 = 0; k4 < BK / UMMA_K; ++k4) {
               umma_bf16_pair(d_tmem, a_desc + ((k4 * a_kstep) >> 4), b_desc + ((k4 * b_kstep) >> 4), idesc,
@@ -374,29 +364,6 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         }
       }
       if (!ok && lane == 0 && p.status) atomicCAS(p.status, ST_OK, ST_TIMEOUT_MMA);
-    } else {
-      if constexpr (kLsuGather) {
-        // Relay: when this CTA's gather threads have filled a stage (their cp.async copies have landed and
-        // arrived on the local gfull barrier), count one arrival on the leader's full barrier.  The remote
-        // arrive is relaxed: a release at cluster scope costs about a microsecond per stage here, and the
-        // copies it would order have already completed when gfull flips.
-        int stage = 0;
-        uint32_t phase = 0;
-        bool ok = true;
-        Tile tile;
-        for (long long t = first_tile; ok && decode_tile<RAGGED_K, DUAL>(p, ss, t, num_n, rank, tile); t += tile_step) {
-          for (int kb = 0; kb < tile.num_kb; ++kb) {
-            if (!mbar_wait(smem_u32(&ss.gfull[stage]), phase, abort_flag)) { ok = false; break; }
-            if (lane == 0) {
-              fence_proxy_async_smem();
-              mbar_arrive_cluster_relaxed(map_to_cta(smem_u32(&ss.full[stage]), 0));
-            }
-            __syncwarp();
-            if (++stage == NSTAGES) { stage = 0; phase ^= 1u; }
-          }
-        }
-        if (!ok && lane == 0 && p.status) atomicCAS(p.status, ST_OK, ST_TIMEOUT_MMA);
-      }
     }
   }
   }  // warps below FIRST_EPI_WARP (DUAL: warps 2 and 3 idle)
@@ -409,7 +376,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       uint32_t phase = 0;
       bool ok = true;
       Tile tile;
-      if constexpr (TG) {
+      {
         // 32 issuing threads (every GATHER_THREADS/32-th thread, so they spread over all gather warps), each
         // fetching 4 rows x 128 B per stage with one gather4.
         constexpr int STRIDE = GATHER_THREADS / 32;
@@ -460,76 +427,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
             }
           }
         }
-      } else
-      for (long long t = first_tile; ok && decode_tile<RAGGED_K, DUAL>(p, ss, t, num_n, rank, tile); t += tile_step) {
-        if constexpr (!RAGGED_K) {
-          // K-major A: 128 rows x 128 B; 8 consecutive threads fetch the 8 pieces of a row
-          static_assert(RAGGED_K || (A_GATHER && !A_MN), "ragged-M kernels gather a K-major A");
-          constexpr int RPP = GATHER_THREADS / 8;
-          constexpr int NPASS = BM / RPP;
-          const int c = gt & 7, rb = gt >> 3;
-          const uint32_t dst_off = rb * 128 + ((c ^ (rb & 7)) << 4);
-          const __nv_bfloat16* src[NPASS];
-#pragma unroll
-          for (int i = 0; i < NPASS; ++i) {
-            const int r = tile.row0 + rb + RPP * i;
-            const int idx = (r < p.total_rows) ? p.gather[r] : 0;
-            src[i] = p.gather_src + static_cast<long long>(idx) * p.gather_ld + c * 8;
-          }
-          for (int kb = 0; kb < tile.num_kb; ++kb) {
-            if (!mbar_wait(smem_u32(&ss.empty[stage]), phase ^ 1u, abort_flag)) { ok = false; break; }
-            const uint32_t dst = smem_u32(sA + stage * A_STAGE_BYTES) + dst_off;
-#pragma unroll
-            for (int i = 0; i < NPASS; ++i) cp_async16(dst + i * (RPP * 128), src[i] + kb * BK, 16);
-            cp_async_arrive_noinc(smem_u32(&ss.gfull[stage]));
-            if (++stage == NSTAGES) { stage = 0; phase ^= 1u; }
-          }
-        } else {
-          // MN-major: one token per 128-byte row; this CTA stages 128 elements of M (A) or N (B) = 2 chunks,
-          // i.e. 16 pieces of 16 B per token, fetched by 16 consecutive threads
-          constexpr int CPR = 16;
-          constexpr int ROWS_PER_PASS = GATHER_THREADS / CPR;
-          constexpr int PASSES = BK / ROWS_PER_PASS;
-          const int cc = gt % CPR, rb = gt / CPR;
-          const int chunk = cc >> 3, c = cc & 7;
-          const int col0 = (A_GATHER ? tile.row0 : tile.n0 + static_cast<int>(rank) * BN_CTA) + cc * 8;
-          const bool col_ok = col0 < (A_GATHER ? p.M : p.N);
-          const __nv_bfloat16* src_col = p.gather_src + col0;
-          uint8_t* stage_base = A_GATHER ? sA : sB;
-          constexpr int STAGE_BYTES = A_GATHER ? A_STAGE_BYTES : B_STAGE_BYTES;
-          // Source rows of three stages are kept in registers, loaded two stages before they are needed, so the
-          // latency of the index loads never sits between "stage is free" and "copies issued".
-          int idx0[PASSES], idx1[PASSES], idx2[PASSES];
-          auto load_idx = [&](int kb, int (&dst_idx)[PASSES]) {
-            const int k0 = tile.k_begin + kb * BK;
-#pragma unroll
-            for (int i = 0; i < PASSES; ++i) {
-              const int tok = k0 + rb + ROWS_PER_PASS * i;
-              dst_idx[i] = (kb < tile.num_kb && tok < tile.k_end && col_ok) ? p.gather[tok] : -1;
-            }
-          };
-          load_idx(0, idx0);
-          load_idx(1, idx1);
-          load_idx(2, idx2);
-          for (int kb = 0; kb < tile.num_kb; ++kb) {
-            if (!mbar_wait(smem_u32(&ss.empty[stage]), phase ^ 1u, abort_flag)) { ok = false; break; }
-            const uint32_t dst = smem_u32(stage_base + stage * STAGE_BYTES) + chunk * CHUNK_BYTES;
-#pragma unroll
-            for (int i = 0; i < PASSES; ++i) {
-              const int r = rb + ROWS_PER_PASS * i;
-              const bool valid = idx0[i] >= 0;
-              const __nv_bfloat16* src = src_col + static_cast<long long>(valid ? idx0[i] : 0) * p.gather_ld;
-              cp_async16(dst + r * 128 + ((c ^ (r & 7)) << 4), src, valid ? 16u : 0u);
-            }
-            cp_async_arrive_noinc(smem_u32(&ss.gfull[stage]));
-#pragma unroll
-            for (int i = 0; i < PASSES; ++i) { idx0[i] = idx1[i]; idx1[i] = idx2[i]; }
-            load_idx(kb + 3, idx2);
-            if (++stage == NSTAGES) { stage = 0; phase ^= 1u; }
-          }
-        }
       }
-      cp_async_wait_all();
       if (!ok && (gt & 31) == 0 && p.status) atomicCAS(p.status, ST_OK, ST_TIMEOUT_PRODUCER);
     }
   }

@@ -10,6 +10,7 @@
 #include <mutex>
 
 #include "../../include/sonicmoe_b200.h"
+#include "device_cache.cuh"
 
 namespace smoe {
 
@@ -407,7 +408,6 @@ __global__ void __launch_bounds__(256) ds_reduce_kernel(const float* __restrict_
 // Scratch of the allocation-free entry point: kMaxSortBlocks x kNoAllocMaxExperts per-chunk bins
 // (512 KiB), resident on every GPU that loads the library until the process exits.
 constexpr int kNoAllocMaxExperts = 1024;
-constexpr int kMaxDevices = 64;
 static __device__ __align__(256) int g_noalloc_hist[kMaxSortBlocks * kNoAllocMaxExperts];
 
 // Device address of g_noalloc_hist on the current device.  In host code the symbol itself is only a
@@ -623,12 +623,14 @@ int smoe_route_metadata(const int* expert_idx, const int* token_idx, long long n
   scan_bins_kernel<<<1, 1024, 0, st>>>(hist, blocks, E, nullptr, expert_count, nullptr, expert_offset);
   if (n > 0) {
     const size_t smem = static_cast<size_t>(E) * (1 + kSortWarps) * sizeof(int);
-    static bool configured = false;
-    if (!configured) {
+    static PerDeviceFlag configured;
+    const int dev = current_device();
+    if (dev < 0) return SMOE_ERR_DRIVER;
+    if (!configured.test(dev)) {
       if (cudaFuncSetAttribute(sort_scatter_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                kMaxSmemExperts * (1 + kSortWarps) * (int)sizeof(int)) != cudaSuccess)
         return SMOE_ERR_LAUNCH;
-      configured = true;
+      configured.set(dev);
     }
     sort_scatter_kernel<<<blocks, kSortThreads, smem, st>>>(expert_idx, n, E, hist, expert_offset, K, token_idx,
                                                             s_scatter_idx, s_reverse_scatter_idx, x_gather_idx);

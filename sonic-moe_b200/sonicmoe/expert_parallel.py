@@ -3,14 +3,23 @@ exchanged with an all-to-all each way (NCCL over NVLink on GPUs).
 
 The reference has no distributed code; this module extends its layer so that the result equals the
 single-device layer applied to every rank's tokens with all E experts.  Rank r owns experts
-[r*E/W, (r+1)*E/W); the router is replicated.  Per forward pass:
+[r*E/W, (r+1)*E/W); the router is replicated.
 
-  1. route locally over the global experts (top-k + softmax, counting sort by expert = by destination rank);
-  2. exchange per-expert row counts (all-to-all of E int32) and read the split sizes on the host;
-  3. dispatch: gather the routed rows of x in grouped order, all-to-all them together with their scores;
-  4. run the local experts on the received rows (the same gather-fused grouped GEMMs; every received row
-     is a "token" with exactly one expert, its output already multiplied by its score);
-  5. return the rows with the reverse all-to-all and sum each token's K rows.
+A token row crosses the link ONCE PER DESTINATION RANK, not once per routed (token, expert) pair: with K
+experts per token spread over W ranks a token reaches at most min(K, W) ranks (K=8 over 8 ranks: 5.2 on
+average, over 2 ranks: 2), and the expert rank adds up the token's local experts before anything travels
+back.  Per forward pass:
+
+  1. route locally over the global experts (top-k + softmax);
+  2. plan: for every destination rank the ascending list of tokens with at least one expert there, and the
+     (token, expert, score) pairs in the same order; exchange the two counts per rank pair and read the split
+     sizes on the host (the one host synchronisation of the layer; the backward pass has none);
+  3. dispatch: gather the listed rows of x (destination-major), all-to-all them; all-to-all the pairs' scores
+     and (row within the sender's segment, local expert) indices;
+  4. run the local experts on the received tokens as a layer with caller-supplied pairs and a variable number
+     of experts per token (the general-routing form of the same gather-fused grouped GEMMs): one output row per
+     received token, already weighted by the scores and summed over that token's local experts;
+  5. return those rows with the reverse all-to-all and add up each token's rows (one per destination rank).
 
 Backward is the mirror image through autograd: every step is an autograd function whose backward is the
 adjoint step (row gather <-> row sum, all-to-all <-> reverse all-to-all); score gradients come out of the
@@ -22,6 +31,8 @@ tensors.  Tests inject a CPU implementation to exercise the multi-rank logic wit
 
 from __future__ import annotations
 
+from dataclasses import dataclass
+
 import torch
 import torch.distributed as dist
 import torch.nn as nn
@@ -31,6 +42,30 @@ from .enums import ActivationType, is_glu
 from .moe import Experts
 
 
+# Exchange timing (benchmarks): while a list is installed here every all-to-all on a CUDA tensor appends a
+# (start, end) pair of CUDA events recorded on the current stream around it.
+_exchange_events: list | None = None
+
+
+def record_exchanges(enable: bool) -> list | None:
+    """Start (True) or stop (False) recording CUDA events around every all-to-all; returns the list that was
+    being filled (pairs of events; read them after a synchronize)."""
+    global _exchange_events
+    prev, _exchange_events = _exchange_events, ([] if enable else None)
+    return prev
+
+
+def _exchange(out, x, out_splits, in_splits, group):
+    if _exchange_events is not None and x.is_cuda:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        dist.all_to_all_single(out, x, out_splits, in_splits, group=group)
+        e1.record()
+        _exchange_events.append((e0, e1))
+    else:
+        dist.all_to_all_single(out, x, out_splits, in_splits, group=group)
+
+
 class _AllToAllRows(torch.autograd.Function):
     """Variable-split all-to-all along dim 0; the backward pass is the same exchange with the splits swapped."""
 
@@ -38,7 +73,7 @@ class _AllToAllRows(torch.autograd.Function):
     def forward(ctx, x, in_splits, out_splits, group):
         x = x.contiguous()
         out = x.new_empty((sum(out_splits),) + tuple(x.shape[1:]))
-        dist.all_to_all_single(out, x, out_splits, in_splits, group=group)
+        _exchange(out, x, out_splits, in_splits, group)
         ctx.in_splits, ctx.out_splits, ctx.group = in_splits, out_splits, group
         return out
 
@@ -46,8 +81,81 @@ class _AllToAllRows(torch.autograd.Function):
     def backward(ctx, g):
         g = g.contiguous()
         back = g.new_empty((sum(ctx.in_splits),) + tuple(g.shape[1:]))
-        dist.all_to_all_single(back, g, ctx.in_splits, ctx.out_splits, group=ctx.group)
+        _exchange(back, g, ctx.in_splits, ctx.out_splits, ctx.group)
         return back, None, None, None
+
+
+@dataclass
+class RowList:
+    """A gather list with its inverse: ``rows[i]`` is the source row of entry i; the entries of source row t are
+    ``rev[offset[t] : offset[t+1]]``.  (The field names the row kernels expect.)"""
+
+    x_gather_idx: torch.Tensor           # (n,) int32 source row of every entry
+    s_reverse_scatter_idx: torch.Tensor  # (n,) int32 entries grouped by source row
+    token_offset: torch.Tensor           # (T+1,) int32
+    K: int = 0
+
+
+@dataclass
+class DispatchPlan:
+    rows: RowList                 # entries = (destination rank, token), destination-major, tokens ascending
+    pair_slot: torch.Tensor       # (P,) int64 flat (token, k) slot of every pair, ordered by (destination, token)
+    pair_row: torch.Tensor        # (P,) int32 position of the pair's token inside its destination's segment
+    pair_expert: torch.Tensor     # (P,) int32 expert id local to the destination rank
+    send_rows: list[int]          # rows sent to / received from every rank
+    recv_rows: list[int]
+    send_pairs: list[int]
+    recv_pairs: list[int]
+
+
+def plan_dispatch(indices: torch.Tensor, num_experts: int, world_size: int, group) -> DispatchPlan:
+    """indices (T, K): global expert of every (token, k) slot.  One device->host read (the split sizes)."""
+    T, K = indices.shape
+    dev = indices.device
+    e_local = num_experts // world_size
+    idx = indices.long()
+    dest = idx // e_local                                                   # (T, K)
+    to_rank = torch.zeros(T, world_size, dtype=torch.bool, device=dev).scatter_(1, dest, True)
+    by_rank = to_rank.t().contiguous()                                      # (W, T)
+    row_counts = by_rank.sum(1)
+    pair_counts = torch.bincount(dest.reshape(-1), minlength=world_size)
+    sent = torch.stack([row_counts, pair_counts], dim=1).to(torch.int32).contiguous()   # (W, 2)
+    received = torch.empty_like(sent)
+    dist.all_to_all_single(received, sent, group=group)
+    host = torch.stack([sent, received]).cpu()                              # the layer's one host synchronisation
+    send_rows, send_pairs = host[0, :, 0].tolist(), host[0, :, 1].tolist()
+    recv_rows, recv_pairs = host[1, :, 0].tolist(), host[1, :, 1].tolist()
+    n = sum(send_rows)
+
+    # entries: positions of the set bits of by_rank in row-major order = destination-major, tokens ascending
+    flat = by_rank.reshape(-1)
+    entry = torch.argsort((~flat).to(torch.uint8), stable=True)[:n]
+    entry_token = (entry % T).to(torch.int32)
+    rev = torch.argsort(entry_token, stable=True).to(torch.int32)
+    per_token = to_rank.sum(1)
+    offset = torch.zeros(T + 1, dtype=torch.int32, device=dev)
+    offset[1:] = per_token.cumsum(0)
+    rows = RowList(entry_token, rev, offset)
+
+    # pairs ordered by (destination, token): the order in which the destination lists them by received row
+    flat_dest = dest.reshape(-1)
+    token_of_slot = torch.arange(T, device=dev).repeat_interleave(K)
+    pair_slot = torch.argsort(flat_dest * T + token_of_slot, stable=True)
+    rank_in_segment = by_rank.long().cumsum(1) - 1                          # (W, T) position of token t in segment d
+    pair_row = rank_in_segment[flat_dest[pair_slot], token_of_slot[pair_slot]].to(torch.int32)
+    pair_expert = (idx.reshape(-1)[pair_slot] % e_local).to(torch.int32)
+    return DispatchPlan(rows, pair_slot, pair_row, pair_expert, send_rows, recv_rows, send_pairs, recv_pairs)
+
+
+def received_pair_tokens(pair_row: torch.Tensor, recv_rows: list[int], recv_pairs: list[int]) -> torch.Tensor:
+    """Row of the receive buffer every received pair refers to: its row inside the sender's segment plus the first
+    row of that segment.  Segments arrive source by source, so the result ascends."""
+    dev = pair_row.device
+    base = torch.tensor([0] + recv_rows[:-1], dtype=torch.int64, device=dev).cumsum(0)
+    src = torch.repeat_interleave(torch.arange(len(recv_pairs), device=dev),
+                                  torch.tensor(recv_pairs, dtype=torch.int64, device=dev),
+                                  output_size=sum(recv_pairs))
+    return (pair_row.long() + base[src]).to(torch.int32)
 
 
 class CudaOps:
@@ -58,25 +166,26 @@ class CudaOps:
 
         return fn.topk_softmax(logits, K)
 
-    def route_metadata(self, expert_idx, E, K):
+    def gather_rows(self, x, rows: RowList):
+        return _GatherRows.apply(x, rows)
+
+    def sum_rows(self, entries, rows: RowList, T):
+        return _SumRows.apply(entries, rows, T)
+
+    def _route(self, tokens, experts, num_local_experts, R):
         from . import functional as fn
 
-        return fn._route_metadata(expert_idx, None, E, K)
+        route = fn._route_metadata(experts, tokens, num_local_experts, 0)
+        route.token_offset = fn._sorted_offsets(tokens, R)
+        return route
 
-    def gather_rows(self, x, route):
-        return _GatherRows.apply(x, route)
-
-    def sum_rows(self, rows, route, T):
-        return _SumRows.apply(rows, route, T)
-
-    def local_experts(self, x_rows, w1, w2, scores, local_expert, num_local_experts, inference):
-        """rows -> score * expert(row); w1 (E_l,2I,H), w2 (E_l,H,I); one expert per row."""
+    def local_layer(self, x_rows, w1, w2, scores, tokens, experts, num_local_experts, inference):
+        """out[r] = sum over the pairs (r, e) of score * expert_e(x_rows[r]); w1 (E_l,2I,H), w2 (E_l,H,I);
+        ``tokens`` ascending."""
         from . import functional as fn
 
         R = x_rows.shape[0]
-        rows = torch.arange(R, dtype=torch.int32, device=x_rows.device)
-        route = fn._route_metadata(local_expert, rows, num_local_experts, 0)
-        route.K = 1  # every received row is its own token with a single routed pair
+        route = self._route(tokens, experts, num_local_experts, R)
         return fn._RoutedExperts.apply(x_rows, w1.permute(1, 2, 0), w2.permute(1, 2, 0), scores, route, R, inference)
 
 
@@ -87,90 +196,64 @@ class Fp8CudaOps(CudaOps):
     def __init__(self, scale_format: str | None = None):
         self.scale_format = scale_format
 
-    def local_experts(self, x_rows, w1, w2, scores, local_expert, num_local_experts, inference):
-        from . import functional as fn
+    def local_layer(self, x_rows, w1, w2, scores, tokens, experts, num_local_experts, inference):
         from .functional.fp8 import _RoutedExpertsFp8
 
         R = x_rows.shape[0]
-        rows = torch.arange(R, dtype=torch.int32, device=x_rows.device)
-        route = fn._route_metadata(local_expert, rows, num_local_experts, 0)
-        route.K = 1
+        route = self._route(tokens, experts, num_local_experts, R)
         return _RoutedExpertsFp8.apply(x_rows, w1.permute(1, 2, 0), w2.permute(1, 2, 0), scores, route, R, inference,
                                        self.scale_format)
 
 
 class _GatherRows(torch.autograd.Function):
-    """out[r] = x[x_gather_idx[r]] (grouped order); backward: dx[t] = sum of the K rows routed from token t."""
+    """out[i] = x[rows.x_gather_idx[i]]; backward: dx[t] = sum of the entries gathered from row t."""
 
     @staticmethod
-    def forward(ctx, x, route):
+    def forward(ctx, x, rows):
         from . import _lib
 
         _lib.require_cuda(x, "x")
         x = x.contiguous()
         T, H = x.shape
-        n = route.x_gather_idx.numel()
+        n = rows.x_gather_idx.numel()
         dev = x.device
         with torch.cuda.device(dev):
             out = torch.empty(n, H, dtype=x.dtype, device=dev)
-            _lib.check(_lib.lib.smoe_gather_sum(x.data_ptr(), out.data_ptr(), None, 0, route.x_gather_idx.data_ptr(),
+            _lib.check(_lib.lib.smoe_gather_sum(x.data_ptr(), out.data_ptr(), None, 0, rows.x_gather_idx.data_ptr(),
                                                 None, n, H, 1, _lib.stream_ptr(dev)), "gather_sum")
-        ctx.route, ctx.T = route, T
+        ctx.rows, ctx.T = rows, T
         return out
 
     @staticmethod
     def backward(ctx, g):
-        return _sum_rows(g.contiguous(), ctx.route, ctx.T), None
+        return _sum_rows(g.contiguous(), ctx.rows, ctx.T), None
 
 
 class _SumRows(torch.autograd.Function):
-    """out[t] = sum_k rows[s_reverse_scatter_idx[t*K+k]]; backward: drows[r] = dout[x_gather_idx[r]]."""
+    """out[t] = sum of the entries of row t; backward: dentries[i] = dout[rows.x_gather_idx[i]]."""
 
     @staticmethod
-    def forward(ctx, rows, route, T):
-        ctx.route = route
-        return _sum_rows(rows.contiguous(), route, T)
+    def forward(ctx, entries, rows, T):
+        ctx.rows = rows
+        return _sum_rows(entries.contiguous(), rows, T)
 
     @staticmethod
     def backward(ctx, g):
-        return _GatherRows.apply(g, ctx.route), None, None
+        return _GatherRows.apply(g, ctx.rows), None, None
 
 
-def _sum_rows(rows, route, T):
+def _sum_rows(entries, rows, T):
     from . import _lib
 
-    _lib.require_cuda(rows, "rows")
-    H = rows.shape[1]
-    dev = rows.device
+    _lib.require_cuda(entries, "rows")
+    H = entries.shape[1]
+    dev = entries.device
     with torch.cuda.device(dev):
-        out = torch.empty(T, H, dtype=rows.dtype, device=dev)
-        _lib.check(_lib.lib.smoe_gather_sum(rows.data_ptr(), out.data_ptr(), None, 0,
-                                            route.s_reverse_scatter_idx.data_ptr(), _lib.ptr(route.token_offset),
-                                            T, H, max(route.K, 1), _lib.stream_ptr(dev)), "gather_sum")
+        out = torch.empty(T, H, dtype=entries.dtype, device=dev)
+        _lib.check(_lib.lib.smoe_gather_sum(entries.data_ptr(), out.data_ptr(), None, 0,
+                                            rows.s_reverse_scatter_idx.data_ptr(), _lib.ptr(rows.token_offset),
+                                            T, H, max(rows.K, 1), _lib.stream_ptr(dev)), "gather_sum")
     return out
-
-
-def dispatch_plan(expert_frequency: torch.Tensor, world_size: int, group) -> tuple[torch.Tensor, list[int], list[int]]:
-    """Exchange per-expert row counts.
-
-    expert_frequency (E,) int32: rows this rank routes to every global expert.  Returns
-    (recv_counts (W, E_l): rows arriving from each source rank for each local expert,
-     send_splits[dst], recv_splits[src]) -- the split sizes of the row all-to-all, read on the host.
-    """
-    E = expert_frequency.numel()
-    e_local = E // world_size
-    recv_counts = torch.empty_like(expert_frequency)
-    dist.all_to_all_single(recv_counts, expert_frequency.contiguous(), group=group)
-    both = torch.stack([expert_frequency.view(world_size, e_local).sum(1),
-                        recv_counts.view(world_size, e_local).sum(1)]).cpu()
-    return recv_counts.view(world_size, e_local), both[0].tolist(), both[1].tolist()
-
-
-def received_row_experts(recv_counts: torch.Tensor) -> torch.Tensor:
-    """Local expert id of every received row: rows arrive source by source, expert by expert within a source."""
-    W, e_local = recv_counts.shape
-    ids = torch.arange(e_local, dtype=torch.int32, device=recv_counts.device).repeat(W)
-    return torch.repeat_interleave(ids, recv_counts.reshape(-1).long())
 
 
 def moe_ep_softmax_topk_layer(x, router_w, w1_local, w2_local, K, num_experts, group=None, ops=None,
@@ -195,20 +278,25 @@ def moe_ep_softmax_topk_layer(x, router_w, w1_local, w2_local, K, num_experts, g
     if logit_bias is not None:
         router_logits = router_logits + logit_bias.to(router_logits.dtype)
     scores, indices = ops.topk_softmax(router_logits, K)
-    route = ops.route_metadata(indices.reshape(-1), num_experts, K)
+    with torch.no_grad():
+        plan = plan_dispatch(indices, num_experts, W, group)
+        expert_frequency = torch.bincount(indices.reshape(-1).long(), minlength=num_experts).to(torch.int32)
 
-    recv_counts, send_splits, recv_splits = dispatch_plan(route.expert_frequency, W, group)
-    x_send = ops.gather_rows(x, route)
-    s_send = scores.reshape(-1)[route.s_scatter_idx.long()]
-    x_recv = _AllToAllRows.apply(x_send, send_splits, recv_splits, group)
-    s_recv = _AllToAllRows.apply(s_send, send_splits, recv_splits, group)
+    x_send = ops.gather_rows(x, plan.rows)
+    s_send = scores.reshape(-1)[plan.pair_slot]
+    x_recv = _AllToAllRows.apply(x_send, plan.send_rows, plan.recv_rows, group)
+    s_recv = _AllToAllRows.apply(s_send, plan.send_pairs, plan.recv_pairs, group)
+    with torch.no_grad():
+        meta = _AllToAllRows.apply(torch.stack([plan.pair_row, plan.pair_expert], dim=1), plan.send_pairs,
+                                   plan.recv_pairs, group)
+        tokens = received_pair_tokens(meta[:, 0], plan.recv_rows, plan.recv_pairs)
+        experts = meta[:, 1].contiguous()
 
-    local_expert = received_row_experts(recv_counts)
-    o_recv = ops.local_experts(x_recv, w1_local, w2_local, s_recv, local_expert, e_local, inference)
+    o_recv = ops.local_layer(x_recv, w1_local, w2_local, s_recv, tokens, experts, e_local, inference)
 
-    y_back = _AllToAllRows.apply(o_recv, recv_splits, send_splits, group)
-    o = ops.sum_rows(y_back, route, T)
-    return o, router_logits, route.expert_frequency
+    o_back = _AllToAllRows.apply(o_recv, plan.recv_rows, plan.send_rows, group)
+    o = ops.sum_rows(o_back, plan.rows, T)
+    return o, router_logits, expert_frequency
 
 
 class ExpertParallelMoE(nn.Module):
@@ -248,12 +336,13 @@ class ExpertParallelMoE(nn.Module):
         self.c_fc.weight.copy_(state["c_fc.weight"][lo:hi])
         self.c_proj.weight.copy_(state["c_proj.weight"][lo:hi])
 
-    def forward(self, hidden_states, is_inference_mode: bool = False):
+    def forward(self, hidden_states, is_inference_mode: bool = False, logit_bias=None):
         shape = hidden_states.shape
         x = hidden_states.view(-1, self.hidden_size)
         o, logits, freq = moe_ep_softmax_topk_layer(
             x, self.router.weight, self.c_fc.weight, self.c_proj.weight, self.top_k, self.num_experts,
-            group=self.group, ops=self.ops, is_inference_mode_enabled=is_inference_mode or not self.training)
+            group=self.group, ops=self.ops, is_inference_mode_enabled=is_inference_mode or not self.training,
+            logit_bias=logit_bias)
         probs = F.softmax(logits, dim=-1, dtype=torch.float32)
         aux = self.num_experts * (F.normalize(probs.sum(0), p=1, dim=0) * F.normalize(freq.float(), p=1, dim=0)).sum()
         return o.view(shape), aux

@@ -42,6 +42,15 @@ def _check_format(fmt: str) -> str:
     return fmt
 
 
+def refuse_unsupported(b1, b2, activation_type) -> None:
+    """The FP8 experts are bias-free SwiGLU only; anything else is refused instead of silently dropping the
+    biases or misreading the up projection's width."""
+    if isinstance(activation_type, str):
+        activation_type = ActivationType(activation_type)
+    if b1 is not None or b2 is not None or activation_type != ActivationType.SWIGLU:
+        raise NotImplementedError("the FP8 expert path is implemented for bias-free SwiGLU experts")
+
+
 def _entry(name: str, fmt: str):
     """The library function ``name`` of the family that takes this scale format."""
     return getattr(lib, ("smoe_fp8_" if fmt == "fp32" else "smoe_mxfp8_") + name)
@@ -240,7 +249,8 @@ def moe_fp8_softmax_topk_layer(x, router_w, w1, b1, w2, b2, K, stream_id=0,
     (``scale_format``: "fp32", "ue8m0" or None for the module default)."""
     from . import _check_experts_args, _route_metadata, topk_softmax
 
-    _check_experts_args(x, w1, w2, b1, b2, activation_type)
+    refuse_unsupported(b1, b2, activation_type)
+    activation_type = _check_experts_args(x, w1, w2, b1, b2, activation_type)
     H = x.shape[1]
     if H % BLOCK != 0 or (w1.shape[0] // 2) % BLOCK != 0:
         raise ValueError("the FP8 path needs hidden and intermediate sizes that are multiples of 128")

@@ -12,7 +12,12 @@ What runs:
     `moe_TC_softmax_topk_layer` by None (unused by the torch backend);
   * `forward_token_choice_rounding` and `ref_moe_token_rounding` from benchmarks/moe-token-rounding.py,
     extracted from the file's source (the script itself imports CUDA-only packages at the top).
+  * `MoE(...).state_dict()` of modules the reference initialised itself (its own `reset_parameters`), stored
+    with an input and the reference's eager output and gradients: the checkpoint-interchange fixtures
+    (`state_dict_*.npz`).
 Inputs come from oracle.moe_oracle.make_inputs (seeded), so the tests can rebuild them.
+
+`python tests/golden/make_golden.py state_dict` regenerates only the fixtures whose name starts with that prefix.
 """
 
 from __future__ import annotations
@@ -43,6 +48,11 @@ LAYER_CASES = [
     ("layer_ties", 160, 64, 64, 16, 4, 1, torch.bfloat16),
     ("layer_k1", 64, 64, 64, 4, 1, 2, torch.bfloat16),
     ("layer_cfg1", 2048, 768, 256, 8, 2, 0, torch.float32),   # BASELINE config 1; only summaries are stored
+]
+# (name, T, H, I, E, K, seed, activation, add_bias): modules initialised by the reference, parameters stored
+STATE_DICT_CASES = [
+    ("state_dict_swiglu", 48, 64, 64, 4, 2, 7, "swiglu", False),
+    ("state_dict_gelu_bias", 48, 64, 128, 4, 2, 8, "gelu", True),
 ]
 ROUNDING_CASES = [
     ("rounding_nr", 512, 64, 64, 8, 2, 3, "nr"),
@@ -106,6 +116,30 @@ def run_layer(moe_mod, enums, T, H, I, E, K, seed, dtype):
                 logits=logits.detach(), expert_frequency=freq.to(torch.int32))
 
 
+def run_state_dict(moe_mod, enums, T, H, I, E, K, seed, act, add_bias):
+    """A module the reference constructs and initialises itself; biases (zero after its reset) get seeded noise so
+    that they matter.  Everything a loader needs is stored: the state dict, x, dout, o, aux and all gradients."""
+    torch.manual_seed(seed)
+    m = moe_mod.MoE(E, K, H, I, enums.ActivationType(act), add_bias, 0.02)
+    if add_bias:
+        with torch.no_grad():
+            m.c_fc.bias.normal_(0, 0.05)
+            m.c_proj.bias.normal_(0, 0.05)
+    with torch.no_grad():  # values a bf16 module can hold exactly, so that a bf16 GPU run sees the same numbers
+        for p in m.parameters():
+            p.copy_(p.bfloat16().float())
+    x = torch.randn(T, H).bfloat16().float().requires_grad_(True)
+    dout = torch.randn(T, H).bfloat16().float()
+    o, aux = m(x, kernel_backend_moe=enums.KernelBackendMoE.torch)
+    names = [n for n, _ in m.named_parameters()]
+    grads = torch.autograd.grad(o, [x] + list(m.parameters()), dout)
+    out = {f"param.{k}": v.detach().numpy() for k, v in m.state_dict().items()}
+    out.update({f"grad.{n}": g.numpy() for n, g in zip(names, grads[1:])})
+    out.update(x=x.detach().numpy(), dout=dout.numpy(), o=o.detach().numpy(), aux_loss=aux.detach().numpy(),
+               dx=grads[0].numpy())
+    return out
+
+
 def summarise(t: torch.Tensor, n=64):
     """A large tensor is stored as (norm, sum, strided sample) instead of in full."""
     flat = t.reshape(-1).double()
@@ -117,7 +151,17 @@ def main():
     torch.manual_seed(0)
     torch.set_num_threads(max(1, os.cpu_count() or 1))
     moe_mod, enums, count_cumsum = load_reference_moe()
+    prefix = sys.argv[1] if len(sys.argv) > 1 else ""
+    for name, T, H, I, E, K, seed, act, add_bias in STATE_DICT_CASES:
+        if not name.startswith(prefix):
+            continue
+        arrays = run_state_dict(moe_mod, enums, T, H, I, E, K, seed, act, add_bias)
+        meta = np.array([T, H, I, E, K, seed, int(add_bias)], dtype=np.int64)
+        np.savez_compressed(os.path.join(HERE, f"{name}.npz"), meta=meta, activation=np.array(act), **arrays)
+        print(name, sorted(k for k in arrays if k.startswith("param.")))
     for name, T, H, I, E, K, seed, dtype in LAYER_CASES:
+        if not name.startswith(prefix):
+            continue
         r = run_layer(moe_mod, enums, T, H, I, E, K, seed, dtype)
         meta = np.array([T, H, I, E, K, seed, 1 if dtype == torch.bfloat16 else 0], dtype=np.int64)
         if T * H > 100_000:
@@ -132,6 +176,8 @@ def main():
 
     route_fn, ref_layer = load_reference_rounding(count_cumsum)
     for name, T, H, I, E, K, seed, routing in ROUNDING_CASES:
+        if not name.startswith(prefix):
+            continue
         inp = make_inputs(T, H, I, E, K, seed=seed, dtype=torch.float32)
         scores, tokens, experts = route_fn(inp["x"], inp["router_w"], E, K, 128, routing)
         o = ref_layer(inp["x"], scores, tokens, experts, inp["w1"], None, inp["w2"], None, E)

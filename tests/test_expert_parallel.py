@@ -24,23 +24,26 @@ class OracleOps:
         idx = torch.sort(logits.float(), dim=-1, descending=True, stable=True).indices[:, :K]
         return torch.softmax(logits.float().gather(-1, idx), dim=-1), idx.to(torch.int32)
 
-    def route_metadata(self, expert_idx, E, K):
-        r = orc.route_metadata(expert_idx, E, expert_idx.numel() // K, K=K)
-        r.K = K
-        return r
+    def gather_rows(self, x, rows):
+        return x[rows.x_gather_idx.long()]
 
-    def gather_rows(self, x, route):
-        return x[route.x_gather_idx.long()]
+    def sum_rows(self, entries, rows, T):
+        # through the inverse list, as the device kernel does, so that a wrong inverse fails here too
+        off = rows.token_offset.tolist()
+        rev = rows.s_reverse_scatter_idx.long()
+        out = [entries[rev[off[t]:off[t + 1]]].sum(0) for t in range(T)]
+        return torch.stack(out) if out else entries.new_zeros(0, entries.shape[1])
 
-    def sum_rows(self, rows, route, T):
-        return rows[route.s_reverse_scatter_idx.long()].view(T, route.K, -1).sum(1)
-
-    def local_experts(self, x_rows, w1, w2, scores, local_expert, num_local_experts, inference):
-        out = torch.zeros_like(x_rows)
+    def local_layer(self, x_rows, w1, w2, scores, tokens, experts, num_local_experts, inference):
+        assert (tokens[1:] >= tokens[:-1]).all()
+        # a function of the rows, the scores and the weights even when no row arrived (as the device layer's autograd node is): every rank
+        # then takes part in the backward exchanges
+        out = x_rows * 0.0 + 0.0 * (w1.sum() + w2.sum() + scores.sum())
         for e in range(num_local_experts):
-            pos = (local_expert == e).nonzero().squeeze(-1)
+            pos = (experts == e).nonzero().squeeze(-1)
             if pos.numel():
-                out = out.index_add(0, pos, (orc.swiglu(x_rows[pos] @ w1[e].T) @ w2[e].T) * scores[pos, None])
+                rows = tokens[pos].long()
+                out = out.index_add(0, rows, (orc.swiglu(x_rows[rows] @ w1[e].T) @ w2[e].T) * scores[pos, None])
         return out
 
 
@@ -56,7 +59,13 @@ def _inputs(world, dtype):
     return full, per_rank
 
 
-def _worker(rank, world, port, backend, outdir, use_cuda):
+def _logit_bias(E_):
+    """The skew of the load-imbalance benchmark at test size: 2 * log(1 / rank) with a seeded permutation of ranks."""
+    g = torch.Generator().manual_seed(5)
+    return 2.0 * torch.log(1.0 / (torch.randperm(E_, generator=g) + 1).float())
+
+
+def _worker(rank, world, port, backend, outdir, use_cuda, use_bias=False):
     import sys
 
     for p in (ROOT, PKG):
@@ -78,7 +87,7 @@ def _worker(rank, world, port, backend, outdir, use_cuda):
         if not use_cuda:
             m.ops = OracleOps()
         x = per_rank[rank]["x"].to(dev).requires_grad_(True)
-        o, aux = m(x)
+        o, aux = m(x, logit_bias=_logit_bias(E).to(dev) if use_bias else None)
         grads = torch.autograd.grad(o, [x, m.router.weight, m.c_fc.weight, m.c_proj.weight],
                                     per_rank[rank]["dout"].to(dev))
         if use_cuda:
@@ -93,9 +102,9 @@ def _worker(rank, world, port, backend, outdir, use_cuda):
         dist.destroy_process_group()
 
 
-def _run_and_check(world, backend, use_cuda, tol):
+def _run_and_check(world, backend, use_cuda, tol, use_bias=False):
     with tempfile.TemporaryDirectory() as outdir:
-        mp.spawn(_worker, args=(world, _free_port(), backend, outdir, use_cuda), nprocs=world, join=True)
+        mp.spawn(_worker, args=(world, _free_port(), backend, outdir, use_cuda, use_bias), nprocs=world, join=True)
         res = [torch.load(os.path.join(outdir, f"rank{r}.pt")) for r in range(world)]
     dtype = torch.bfloat16 if use_cuda else torch.float32
     full, per_rank = _inputs(world, dtype)
@@ -103,9 +112,13 @@ def _run_and_check(world, backend, use_cuda, tol):
     x_all = torch.cat([p["x"].float() for p in per_rank])
     dout_all = torch.cat([p["dout"].float() for p in per_rank])
     logits = None
-    if use_cuda:  # route the oracle on the logits the device computed (bf16 linear)
-        logits = torch.cat([torch.nn.functional.linear(p["x"].cuda(), full["router_w"].cuda()).float().cpu()
-                            for p in per_rank])
+    if use_cuda:  # route the oracle on the logits the device computed (bf16 linear, bf16 bias add)
+        logits = torch.cat([torch.nn.functional.linear(p["x"].cuda(), full["router_w"].cuda()) for p in per_rank])
+        if use_bias:
+            logits = logits + _logit_bias(E).cuda().to(logits.dtype)
+        logits = logits.float().cpu()
+    elif use_bias:
+        logits = x_all @ f32["router_w"].T + _logit_bias(E)
     ref = orc.moe_layer(x_all, f32["router_w"], f32["w1"], f32["w2"], K, dout=dout_all, logits=logits)
 
     def rel(a, b):
@@ -131,17 +144,123 @@ def test_expert_parallel_host_logic_gloo(built_library, world):
     _run_and_check(world, "gloo", use_cuda=False, tol=1e-5)
 
 
-def test_dispatch_plan_helpers():
-    from sonicmoe.expert_parallel import received_row_experts
+def test_received_pair_tokens():
+    from sonicmoe.expert_parallel import received_pair_tokens
 
-    counts = torch.tensor([[2, 0, 1], [0, 3, 1]], dtype=torch.int32)  # (W=2, E_l=3)
-    assert received_row_experts(counts).tolist() == [0, 0, 2, 1, 1, 1, 2]
-    assert received_row_experts(torch.zeros(2, 3, dtype=torch.int32)).numel() == 0
+    # two sources: 3 rows / 4 pairs from rank 0, 2 rows / 2 pairs from rank 1
+    rows = received_pair_tokens(torch.tensor([0, 0, 1, 2, 0, 1], dtype=torch.int32), [3, 2], [4, 2])
+    assert rows.tolist() == [0, 0, 1, 2, 3, 4]
+    assert received_pair_tokens(torch.zeros(0, dtype=torch.int32), [0, 0], [0, 0]).numel() == 0
+
+
+def _idle_rank_worker(rank, world, port, outdir):
+    """Every token of every rank picks experts of rank 0 only: rank 1 receives no rows and still has to take part
+    in every exchange and return zero gradients for its experts."""
+    import sys
+
+    for p in (ROOT, PKG):
+        if p not in sys.path:
+            sys.path.insert(0, p)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from sonicmoe.expert_parallel import moe_ep_softmax_topk_layer
+
+        full, per_rank = _inputs(world, torch.float32)
+        e_local = E // world
+        bias = torch.zeros(E)
+        bias[:e_local] = 100.0
+        x = per_rank[rank]["x"].clone().requires_grad_(True)
+        w1 = full["w1"][rank * e_local:(rank + 1) * e_local].clone().requires_grad_(True)
+        w2 = full["w2"][rank * e_local:(rank + 1) * e_local].clone().requires_grad_(True)
+        o, logits, freq = moe_ep_softmax_topk_layer(x, full["router_w"], w1, w2, K, E, ops=OracleOps(), logit_bias=bias)
+        grads = torch.autograd.grad(o, [x, w1, w2], per_rank[rank]["dout"])
+        torch.save({"o": o.detach(), "logits": logits.detach(), "grads": grads}, os.path.join(outdir, f"rank{rank}.pt"))
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_expert_parallel_rank_without_rows_gloo(built_library):
+    world = 2
+    with tempfile.TemporaryDirectory() as outdir:
+        mp.spawn(_idle_rank_worker, args=(world, _free_port(), outdir), nprocs=world, join=True)
+        res = [torch.load(os.path.join(outdir, f"rank{r}.pt")) for r in range(world)]
+    full, per_rank = _inputs(world, torch.float32)
+    x_all = torch.cat([p["x"] for p in per_rank])
+    dout_all = torch.cat([p["dout"] for p in per_rank])
+    logits = torch.cat([r["logits"] for r in res])
+    ref = orc.moe_layer(x_all, full["router_w"], full["w1"], full["w2"], K, dout=dout_all, logits=logits)
+    assert ref["expert_frequency"][E // world:].sum() == 0
+    n0 = TOKENS[0]
+    e_local = E // world
+    for r, sl in ((0, slice(0, n0)), (1, slice(n0, n0 + TOKENS[1]))):
+        assert (res[r]["o"] - ref["o"][sl]).norm() <= 1e-5 * ref["o"][sl].norm()
+        assert (res[r]["grads"][0] - ref["dx"][sl]).norm() <= 1e-5 * ref["dx"][sl].norm()
+    assert (res[0]["grads"][1] - ref["dw1"][:e_local]).norm() <= 1e-5 * ref["dw1"][:e_local].norm()
+    assert (res[1]["grads"][1] == 0).all() and (res[1]["grads"][2] == 0).all()
+
+
+def test_expert_parallel_logit_bias_gloo(built_library):
+    _run_and_check(2, "gloo", use_cuda=False, tol=1e-5, use_bias=True)
 
 
 @pytest.mark.gpu
-def test_expert_parallel_single_rank_cuda(built_library):
-    _run_and_check(1, "nccl", use_cuda=True, tol=1e-2)
+@pytest.mark.parametrize("use_bias", [False, True])
+def test_expert_parallel_single_rank_cuda(built_library, use_bias):
+    _run_and_check(1, "nccl", use_cuda=True, tol=1e-2, use_bias=use_bias)
+
+
+def _fp8_worker(rank, world, port, outdir, fmt):
+    """The expert-parallel layer with the FP8 device ops beside the single-device FP8 layer on the same inputs."""
+    import sys
+
+    for p in (ROOT, PKG):
+        if p not in sys.path:
+            sys.path.insert(0, p)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world)
+    try:
+        from sonicmoe import _lib
+        from sonicmoe.expert_parallel import Fp8CudaOps, moe_ep_softmax_topk_layer
+        from sonicmoe.functional.fp8 import moe_fp8_softmax_topk_layer
+
+        T_, H_, I_, E_, K_ = 600, 256, 128, 8, 2
+        inp = orc.make_inputs(T_, H_, I_, E_, K_, seed=21, dtype=torch.bfloat16)
+        dev = torch.device("cuda", rank)
+        leaves = {k: inp[k].to(dev).requires_grad_(True) for k in ("x", "router_w", "w1", "w2")}
+        o, logits, freq = moe_ep_softmax_topk_layer(leaves["x"], leaves["router_w"], leaves["w1"], leaves["w2"], K_, E_,
+                                                    ops=Fp8CudaOps(fmt))
+        grads = torch.autograd.grad(o, list(leaves.values()), inp["dout"].to(dev))
+        o2, _, freq2 = moe_fp8_softmax_topk_layer(leaves["x"], leaves["router_w"], leaves["w1"].permute(1, 2, 0), None,
+                                                  leaves["w2"].permute(1, 2, 0), None, K_, scale_format=fmt)
+        grads2 = torch.autograd.grad(o2, list(leaves.values()), inp["dout"].to(dev))
+        torch.cuda.synchronize()
+        _lib.check_status()
+        torch.save({"ep": [o.detach().float().cpu()] + [g.float().cpu() for g in grads],
+                    "single": [o2.detach().float().cpu()] + [g.float().cpu() for g in grads2],
+                    "freq": (freq.cpu(), freq2.cpu()), "logits": logits.detach().float().cpu()},
+                   os.path.join(outdir, "rank0.pt"))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("fmt", ["fp32", "ue8m0"])
+def test_expert_parallel_fp8_ops_single_rank_cuda(built_library, fmt):
+    """`Fp8CudaOps` (what the FP8 expert-parallel benchmark runs): equal to the single-device FP8 layer on the same
+    inputs, and as close to the fp32 oracle as that layer is (E4M3 x E4M3 products: see test_fp8_gpu.py)."""
+    with tempfile.TemporaryDirectory() as outdir:
+        mp.spawn(_fp8_worker, args=(1, _free_port(), outdir, fmt), nprocs=1, join=True)
+        res = torch.load(os.path.join(outdir, "rank0.pt"))
+    assert torch.equal(res["freq"][0], res["freq"][1])
+    inp = {k: v.float() for k, v in orc.make_inputs(600, 256, 128, 8, 2, seed=21, dtype=torch.bfloat16).items()}
+    ref = orc.moe_layer(inp["x"], inp["router_w"], inp["w1"], inp["w2"], 2, dout=inp["dout"], logits=res["logits"])
+    want = [ref["o"], ref["dx"], ref["drouter_w"], ref["dw1"], ref["dw2"]]
+    for got_ep, got_single, w in zip(res["ep"], res["single"], want):
+        assert (got_ep - got_single).norm() <= 2e-2 * got_single.norm()
+        assert (got_ep - w).norm() <= 9e-2 * w.norm()
 
 
 @pytest.mark.gpu

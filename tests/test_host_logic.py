@@ -1,5 +1,6 @@
 """Host-side logic that needs no GPU: module surface, state-dict layout, eager backend vs oracle, errors."""
 
+import numpy as np
 import pytest
 import torch
 
@@ -100,3 +101,49 @@ def test_token_rounding_router_has_no_cpu_path():
         forward_token_choice_rounding(inp["x"], inp["router_w"], 8, 2, 128, "nr")
     with pytest.raises(NotImplementedError):
         select_pairs(torch.zeros(4, 8), torch.zeros(4, 2, dtype=torch.int32), "sideways")
+
+
+@pytest.mark.parametrize("name", ["state_dict_swiglu", "state_dict_gelu_bias"])
+def test_reference_state_dict_loads_and_reproduces_reference_output(built_library, name):
+    """Checkpoint interchange: the state dict of a module the reference constructed and initialised loads with
+    strict=True into this build's `MoE`, and the eager backend then reproduces the reference's output, aux loss and
+    every gradient (fixtures: tests/golden/make_golden.py, reference sonicmoe/moe.py:58-68, 186-204)."""
+    import sonicmoe
+    from conftest import golden
+    from sonicmoe import KernelBackendMoE
+    from sonicmoe.enums import ActivationType
+
+    g = golden(name)
+    T, H, I, E, K, _seed, add_bias = [int(v) for v in g["meta"]]
+    state = {k[len("param."):]: torch.from_numpy(g[k]) for k in g.files if k.startswith("param.")}
+    m = sonicmoe.MoE(E, K, H, I, ActivationType(str(g["activation"])), bool(add_bias), 0.02)
+    missing = m.load_state_dict(state, strict=True)
+    assert not missing.missing_keys and not missing.unexpected_keys
+    x = torch.from_numpy(g["x"]).requires_grad_(True)
+    o, aux = m(x, kernel_backend_moe=KernelBackendMoE.torch)
+    names = [n for n, _ in m.named_parameters()]
+    grads = torch.autograd.grad(o, [x] + list(m.parameters()), torch.from_numpy(g["dout"]))
+
+    def close(a, b):
+        b = torch.from_numpy(np.asarray(b))
+        assert (a.detach() - b).norm() <= 2e-5 * b.norm() + 1e-12
+
+    close(o, g["o"])
+    close(aux, g["aux_loss"])
+    close(grads[0], g["dx"])
+    for n, got in zip(names, grads[1:]):
+        close(got, g[f"grad.{n}"])
+
+
+def test_fp8_layer_refuses_biases_and_other_activations(built_library):
+    """The FP8 experts are bias-free SwiGLU: other configurations are refused, not silently mis-computed."""
+    from sonicmoe.functional.fp8 import moe_fp8_softmax_topk_layer
+
+    m, inp = _module()
+    w1 = m.c_fc.weight.permute(1, 2, 0)
+    w2 = m.c_proj.weight.permute(1, 2, 0)
+    b1, b2 = torch.zeros(8, 128), torch.zeros(8, 128)
+    with pytest.raises(NotImplementedError):
+        moe_fp8_softmax_topk_layer(inp["x"], m.router.weight, w1, b1, w2, b2, 2)
+    with pytest.raises(NotImplementedError):
+        moe_fp8_softmax_topk_layer(inp["x"], m.router.weight, w1, None, w2, None, 2, 0, "geglu")

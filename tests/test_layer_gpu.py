@@ -274,3 +274,25 @@ def test_bias_and_activations_vs_oracle(built_library, act, bias):
     if bias:
         assert rel(grads[3], ref["db1"]) < TOL
         assert rel(grads[4], ref["db2"]) < TOL
+
+
+def test_second_device_in_one_process(built_library):
+    """Kernel attributes (dynamic shared memory) and the SM count are cached per device, not per process: a layer on
+    cuda:1 of a process that already ran one on cuda:0 launches and gives the same result."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    from sonicmoe import _lib
+
+    T, H, I, E, K = 512, 256, 128, 16, 4
+    outs = []
+    for d in (0, 1):
+        m, inp = _module(T, H, I, E, K, seed=3)
+        m = m.to(f"cuda:{d}")
+        x = inp["x"].to(f"cuda:{d}").requires_grad_(True)
+        o, _ = m(x)
+        o.backward(inp["dout"].to(f"cuda:{d}"))
+        torch.cuda.synchronize(d)
+        _lib.check_status(torch.device("cuda", d))
+        outs.append((o.detach().cpu(), x.grad.cpu(), m.c_fc.weight.grad.cpu()))
+    for a, b in zip(*outs):
+        assert torch.equal(a, b)
