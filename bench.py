@@ -731,7 +731,11 @@ def run_ep_arm(args, rank, world, local_rank, workload):
             "vs_baseline": None, "dtype": "fp8_e4m3 (weight gradients bf16)" if fp8 else "bf16", "data": "synthetic",
             "tokens_per_s": world * T / (ms_per_step * 1e-3), "tflops_per_gpu": value / world,
             "config": {"workload": label, **cfg, "tokens": "T per GPU", "parallelism": f"ep{world}",
-                       "collective": "NCCL all_to_all_single (token rows once per destination rank, scores, indices)",
+                       "collective": ("token rows once per destination rank over peer memory (own gather-and-store "
+                                      "kernel + copy-engine copies, NCCL one-element all-reduce as the barrier); "
+                                      "scores and indices by NCCL all_to_all_single"
+                                      if world > 1 and os.environ.get("SONICMOE_EP_TRANSPORT", "peer") == "peer" else
+                                      "NCCL all_to_all_single (token rows once per destination rank, scores, indices)"),
                        "routing": "softmax_topk" + (" + per-expert logit bias 2*log(1/rank)" if zipf else ""),
                        "l2_policy": "inputs larger than L2"},
             **({"fp8_scale_format": args.fp8_scales} if fp8 else {}),
@@ -759,6 +763,7 @@ def run_ep_arm(args, rank, world, local_rank, workload):
         line["cpu_baseline"] = None  # N = 1 only
         print(json.dumps(line), flush=True)
     dist.barrier()
+    ep.close_default_transports()
     dist.destroy_process_group()
 
 

@@ -326,6 +326,36 @@ int smoe_mxfp8_up_projection_backward_dx_rows(const void* dzq, const void* dz_sc
                                               const int* x_gather_idx, int H, int I, int E, int TK, int* status,
                                               void* stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * Expert parallelism over peer memory (one node, NVLink / NVSwitch).  The reference has no distributed
+ * code (sonicmoe/moe.py:260 skips even the aux-loss reduction), so these have no counterpart there; they
+ * carry the dispatch / combine exchange of an expert-sharded layer.
+ * ------------------------------------------------------------------------------------------- */
+enum { SMOE_MAX_PEERS = 16, SMOE_PEER_HANDLE_BYTES = 64 };
+
+/* A device buffer other processes of the node can map (cudaMalloc + zero fill) and its release.  These two are
+ * the only functions of the library that allocate; every rank calls them once per exchange buffer, not per step. */
+int smoe_peer_alloc(size_t bytes, void** ptr /* host out */);
+int smoe_peer_free(void* ptr);
+/* CUDA IPC: export a smoe_peer_alloc buffer as 64 opaque bytes (host memory) to hand to the other ranks; map a
+ * buffer another rank exported (peer access to its GPU is enabled on first use); unmap it. */
+int smoe_peer_export(const void* ptr, unsigned char* handle64 /* host out */);
+int smoe_peer_open(const unsigned char* handle64 /* host */, void** ptr /* host out */);
+int smoe_peer_close(void* ptr);
+/* Stream-ordered copy of a contiguous segment between any two device buffers (local or mapped peer memory);
+ * runs on a copy engine, leaves the multiprocessors to the GEMMs. */
+int smoe_peer_copy(void* dst, const void* src, size_t bytes, void* stream);
+/* smoe_gather_sum whose output rows are cut into num_segments consecutive segments, each written to its own
+ * destination: output row t of segment s (segment_start[s] <= t < segment_start[s+1]) goes to row
+ * t - segment_start[s] of the (rows, H) bf16 buffer segment_ptr[s], which may be mapped peer memory (16-byte
+ * peer stores).  With K = 1 and no weights it is the dispatch of routed token rows fused with their gather;
+ * with token_offset it is the return of per-token sums fused with the reduction.  segment_ptr (num_segments)
+ * and segment_start (num_segments + 1, first 0, last T) are HOST arrays; num_segments <= SMOE_MAX_PEERS.
+ * The caller orders the ranks (a barrier after the launch) before anybody reads what was written. */
+int smoe_gather_sum_to_peers(const void* src, const void* weights, int weights_dtype, const int* reverse_idx,
+                             const int* token_offset, int T, int H, int K, void* const* segment_ptr /* host */,
+                             const int* segment_start /* host */, int num_segments, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -79,6 +79,13 @@ SIGNATURES: dict[str, tuple] = {
     "smoe_mxfp8_down_projection_backward_act": (I, [P, P, P, P, P, P, I, P, P, P, P, P, P, I, I, I, I, I, P, P]),
     "smoe_mxfp8_down_projection_backward_act_q": (I, [P, P, P, P, P, P, I, P, P, P, P, P, P, P, P, I, I, I, I, I, P, P]),
     "smoe_mxfp8_up_projection_backward_dx": (I, [P, P, P, P, P, P, I, I, I, I, P, P]),
+    "smoe_peer_alloc": (I, [c_size_t, P]),
+    "smoe_peer_free": (I, [P]),
+    "smoe_peer_export": (I, [P, P]),
+    "smoe_peer_open": (I, [P, P]),
+    "smoe_peer_close": (I, [P]),
+    "smoe_peer_copy": (I, [P, P, c_size_t, P]),
+    "smoe_gather_sum_to_peers": (I, [P, P, I, P, P, I, I, I, P, P, I, P]),
 }
 
 

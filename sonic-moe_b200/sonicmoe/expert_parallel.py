@@ -14,12 +14,15 @@ back.  Per forward pass:
   2. plan: for every destination rank the ascending list of tokens with at least one expert there, and the
      (token, expert, score) pairs in the same order; exchange the two counts per rank pair and read the split
      sizes on the host (the one host synchronisation of the layer; the backward pass has none);
-  3. dispatch: gather the listed rows of x (destination-major), all-to-all them; all-to-all the pairs' scores
-     and (row within the sender's segment, local expert) indices;
+  3. dispatch: the listed rows of x go to their destination ranks -- over peer memory by default: one kernel
+     gathers each row and stores it straight into the destination's exchange buffer (sonicmoe/peer.py); or an
+     NCCL / gloo all-to-all of the gathered rows; the pairs' scores and (row within the sender's segment, local
+     expert) indices follow by all-to-all (a few bytes per pair);
   4. run the local experts on the received tokens as a layer with caller-supplied pairs and a variable number
      of experts per token (the general-routing form of the same gather-fused grouped GEMMs): one output row per
      received token, already weighted by the scores and summed over that token's local experts;
-  5. return those rows with the reverse all-to-all and add up each token's rows (one per destination rank).
+  5. return those rows (copy-engine copies into the source ranks' buffers, or the reverse all-to-all) and add up
+     each token's rows (one per destination rank).
 
 Backward is the mirror image through autograd: every step is an autograd function whose backward is the
 adjoint step (row gather <-> row sum, all-to-all <-> reverse all-to-all); score gradients come out of the
@@ -55,15 +58,20 @@ def record_exchanges(enable: bool) -> list | None:
     return prev
 
 
+def _timed_exchange(fn, on_cuda: bool):
+    """Run fn(); while recording is on, between two CUDA events on the current stream."""
+    if _exchange_events is None or not on_cuda:
+        return fn()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    out = fn()
+    e1.record()
+    _exchange_events.append((e0, e1))
+    return out
+
+
 def _exchange(out, x, out_splits, in_splits, group):
-    if _exchange_events is not None and x.is_cuda:
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        dist.all_to_all_single(out, x, out_splits, in_splits, group=group)
-        e1.record()
-        _exchange_events.append((e0, e1))
-    else:
-        dist.all_to_all_single(out, x, out_splits, in_splits, group=group)
+    _timed_exchange(lambda: dist.all_to_all_single(out, x, out_splits, in_splits, group=group), x.is_cuda)
 
 
 class _AllToAllRows(torch.autograd.Function):
@@ -106,6 +114,10 @@ class DispatchPlan:
     recv_rows: list[int]
     send_pairs: list[int]
     recv_pairs: list[int]
+    # where segments land when ranks write into each other's buffers (peer transport); rows
+    dispatch_offset: list[int]    # [d]: first row, in rank d's receive buffer, of the segment this rank sends to d
+    return_offset: list[int]      # [s]: first row, in rank s's entry list, of the segment rank s sent here
+    token_capacity: int           # most tokens any rank holds: a rank receives at most world_size * this many rows
 
 
 def plan_dispatch(indices: torch.Tensor, num_experts: int, world_size: int, group) -> DispatchPlan:
@@ -119,12 +131,21 @@ def plan_dispatch(indices: torch.Tensor, num_experts: int, world_size: int, grou
     by_rank = to_rank.t().contiguous()                                      # (W, T)
     row_counts = by_rank.sum(1)
     pair_counts = torch.bincount(dest.reshape(-1), minlength=world_size)
-    sent = torch.stack([row_counts, pair_counts], dim=1).to(torch.int32).contiguous()   # (W, 2)
-    received = torch.empty_like(sent)
-    dist.all_to_all_single(received, sent, group=group)
-    host = torch.stack([sent, received]).cpu()                              # the layer's one host synchronisation
-    send_rows, send_pairs = host[0, :, 0].tolist(), host[0, :, 1].tolist()
-    recv_rows, recv_pairs = host[1, :, 0].tolist(), host[1, :, 1].tolist()
+    # every rank learns every rank's counts (and token count): rows[s][d], pairs[s][d] from rank s to rank d
+    mine = torch.cat([row_counts, pair_counts, row_counts.new_tensor([T])]).to(torch.int32)
+    everyone = torch.empty(world_size * (2 * world_size + 1), dtype=torch.int32, device=dev)
+    dist.all_gather_into_tensor(everyone, mine, group=group)
+    host = everyone.view(world_size, 2 * world_size + 1).cpu().tolist()                                          # the layer's one host synchronisation
+    me = dist.get_rank(group)
+    W = world_size
+    rows_sd = [h[:W] for h in host]
+    pairs_sd = [h[W:2 * W] for h in host]
+    send_rows, send_pairs = rows_sd[me], pairs_sd[me]
+    recv_rows = [rows_sd[s][me] for s in range(W)]
+    recv_pairs = [pairs_sd[s][me] for s in range(W)]
+    dispatch_offset = [sum(rows_sd[s][d] for s in range(me)) for d in range(W)]
+    return_offset = [sum(rows_sd[s][d] for d in range(me)) for s in range(W)]
+    token_capacity = max(h[2 * W] for h in host)
     n = sum(send_rows)
 
     # entries: positions of the set bits of by_rank in row-major order = destination-major, tokens ascending
@@ -144,7 +165,8 @@ def plan_dispatch(indices: torch.Tensor, num_experts: int, world_size: int, grou
     rank_in_segment = by_rank.long().cumsum(1) - 1                          # (W, T) position of token t in segment d
     pair_row = rank_in_segment[flat_dest[pair_slot], token_of_slot[pair_slot]].to(torch.int32)
     pair_expert = (idx.reshape(-1)[pair_slot] % e_local).to(torch.int32)
-    return DispatchPlan(rows, pair_slot, pair_row, pair_expert, send_rows, recv_rows, send_pairs, recv_pairs)
+    return DispatchPlan(rows, pair_slot, pair_row, pair_expert, send_rows, recv_rows, send_pairs, recv_pairs,
+                        dispatch_offset, return_offset, token_capacity)
 
 
 def received_pair_tokens(pair_row: torch.Tensor, recv_rows: list[int], recv_pairs: list[int]) -> torch.Tensor:
@@ -256,8 +278,111 @@ def _sum_rows(entries, rows, T):
     return out
 
 
+class CollectiveTransport:
+    """Token rows by `all_to_all_single` of the process group's backend (NCCL on GPUs, gloo in the CPU tests)."""
+
+    def __init__(self, group, ops):
+        self.group, self.ops = group, ops
+
+    def dispatch(self, x, plan, keep):
+        return _AllToAllRows.apply(self.ops.gather_rows(x, plan.rows), plan.send_rows, plan.recv_rows, self.group)
+
+    def combine(self, rows, plan, T):
+        back = _AllToAllRows.apply(rows, plan.recv_rows, plan.send_rows, self.group)
+        return self.ops.sum_rows(back, plan.rows, T)
+
+
+class _Lease:
+    """Gives a slot of the peer transport's receive buffer back when the autograd graph that reads it goes away."""
+
+    def __init__(self, transport, slot):
+        self.transport, self.slot = transport, slot
+
+    def __del__(self):
+        self.transport.release_slot(self.slot)
+
+
+class _PeerDispatch(torch.autograd.Function):
+    """x (T,H) -> the rows this rank's experts need, written by their owners straight into this rank's exchange
+    buffer (gather fused with the send); backward: the row gradients go back and each token's are added up."""
+
+    @staticmethod
+    def forward(ctx, x, plan, transport, keep):
+        slot = transport.take_slot(keep)
+        if keep:
+            ctx.lease = _Lease(transport, slot)
+        ctx.plan, ctx.transport, ctx.T = plan, transport, x.shape[0]
+        return _timed_exchange(lambda: transport.dispatch_rows(x, plan, ("dispatch_fwd", slot)), True)
+
+    @staticmethod
+    def backward(ctx, g):
+        back = _timed_exchange(lambda: ctx.transport.return_rows(g, ctx.plan, ("return_bwd",)), True)
+        ctx.lease = None
+        return _sum_rows(back, ctx.plan.rows, ctx.T), None, None, None
+
+
+class _PeerCombine(torch.autograd.Function):
+    """The expert ranks' per-token partial sums back to the tokens' ranks and added up there; backward: the output
+    gradient's rows dispatched to the expert ranks (the same fused gather + send)."""
+
+    @staticmethod
+    def forward(ctx, rows, plan, transport, T):
+        ctx.plan, ctx.transport = plan, transport
+        back = _timed_exchange(lambda: transport.return_rows(rows, plan, ("return_fwd",)), True)
+        return _sum_rows(back, plan.rows, T)
+
+    @staticmethod
+    def backward(ctx, g):
+        return _timed_exchange(lambda: ctx.transport.dispatch_rows(g, ctx.plan, ("dispatch_bwd",)), True), None, None, None
+
+
+class PeerMemoryTransport:
+    """Token rows through buffers the ranks map from each other (sonicmoe/peer.py): the library's own kernels and
+    copy-engine copies over NVLink instead of an NCCL all-to-all.  bf16 CUDA rows, one node."""
+
+    def __init__(self, group, device, depth: int = 2):
+        from .peer import PeerTransport
+
+        self.impl = PeerTransport(group, device, depth)
+
+    def dispatch(self, x, plan, keep):
+        return _PeerDispatch.apply(x, plan, self.impl, keep)
+
+    def combine(self, rows, plan, T):
+        return _PeerCombine.apply(rows, plan, self.impl, T)
+
+    def close(self):
+        self.impl.close()
+
+
+_default_transports: dict = {}
+
+
+def default_transport(group, x, ops):
+    """Peer memory for bf16 CUDA rows on more than one rank (SONICMOE_EP_TRANSPORT=nccl selects the collective),
+    the collective otherwise.  One peer transport per (process group, device) is kept for functional callers."""
+    import os
+
+    W = dist.get_world_size(group)
+    use_peer = (x.is_cuda and x.dtype == torch.bfloat16 and W > 1
+                and os.environ.get("SONICMOE_EP_TRANSPORT", "peer") == "peer")
+    if not use_peer:
+        return CollectiveTransport(group, ops)
+    key = (id(group) if group is not None else None, x.device.index)
+    if key not in _default_transports:
+        _default_transports[key] = PeerMemoryTransport(group, x.device)
+    return _default_transports[key]
+
+
+def close_default_transports() -> None:
+    """Collective: release the peer-memory buffers of the default transports (before destroying the process group)."""
+    for t in _default_transports.values():
+        t.close()
+    _default_transports.clear()
+
+
 def moe_ep_softmax_topk_layer(x, router_w, w1_local, w2_local, K, num_experts, group=None, ops=None,
-                              is_inference_mode_enabled=False, logit_bias=None):
+                              is_inference_mode_enabled=False, logit_bias=None, transport=None):
     """Expert-parallel token-choice top-K layer.
 
     x (T_local,H); router_w (E,H) replicated; w1_local (E/W,2I,H), w2_local (E/W,H,I): this rank's experts.
@@ -282,9 +407,9 @@ def moe_ep_softmax_topk_layer(x, router_w, w1_local, w2_local, K, num_experts, g
         plan = plan_dispatch(indices, num_experts, W, group)
         expert_frequency = torch.bincount(indices.reshape(-1).long(), minlength=num_experts).to(torch.int32)
 
-    x_send = ops.gather_rows(x, plan.rows)
+    transport = transport or default_transport(group, x, ops)
+    x_recv = transport.dispatch(x, plan, keep=not inference)
     s_send = scores.reshape(-1)[plan.pair_slot]
-    x_recv = _AllToAllRows.apply(x_send, plan.send_rows, plan.recv_rows, group)
     s_recv = _AllToAllRows.apply(s_send, plan.send_pairs, plan.recv_pairs, group)
     with torch.no_grad():
         meta = _AllToAllRows.apply(torch.stack([plan.pair_row, plan.pair_expert], dim=1), plan.send_pairs,
@@ -294,8 +419,7 @@ def moe_ep_softmax_topk_layer(x, router_w, w1_local, w2_local, K, num_experts, g
 
     o_recv = ops.local_layer(x_recv, w1_local, w2_local, s_recv, tokens, experts, e_local, inference)
 
-    o_back = _AllToAllRows.apply(o_recv, plan.recv_rows, plan.send_rows, group)
-    o = ops.sum_rows(o_back, plan.rows, T)
+    o = transport.combine(o_recv, plan, T)
     return o, router_logits, expert_frequency
 
 
@@ -327,6 +451,7 @@ class ExpertParallelMoE(nn.Module):
         self.c_fc = Experts(self.num_local_experts, hidden_size, up, add_bias=False, std=std)
         self.c_proj = Experts(self.num_local_experts, intermediate_size, hidden_size, add_bias=False, std=std)
         self.ops = None  # CudaOps unless a test injects another implementation
+        self.transport = None  # default_transport() unless set (a module with its own PeerMemoryTransport)
 
     @torch.no_grad()
     def load_full_state_dict(self, state: dict) -> None:
@@ -342,7 +467,7 @@ class ExpertParallelMoE(nn.Module):
         o, logits, freq = moe_ep_softmax_topk_layer(
             x, self.router.weight, self.c_fc.weight, self.c_proj.weight, self.top_k, self.num_experts,
             group=self.group, ops=self.ops, is_inference_mode_enabled=is_inference_mode or not self.training,
-            logit_bias=logit_bias)
+            logit_bias=logit_bias, transport=self.transport)
         probs = F.softmax(logits, dim=-1, dtype=torch.float32)
         aux = self.num_experts * (F.normalize(probs.sum(0), p=1, dim=0) * F.normalize(freq.float(), p=1, dim=0)).sum()
         return o.view(shape), aux

@@ -1,0 +1,173 @@
+"""Peer-memory transport of the expert-parallel layer (one node, NVLink / NVSwitch).
+
+Every rank owns a few exchange buffers that the other ranks map through CUDA IPC (`smoe_peer_*` in the library).
+Token rows then move with the library's own kernels and copy-engine copies instead of an NCCL all-to-all:
+
+* dispatch: `smoe_gather_sum_to_peers` gathers the routed rows and stores each one directly into its destination
+  rank's buffer (the gather and the send are one kernel, no staging copy);
+* combine: the rows an expert rank computed for another rank's tokens are contiguous per source rank, so they go
+  back with one copy-engine copy per peer (`smoe_peer_copy`), and the source adds up each token's rows.
+
+After the writes of an exchange every rank joins a one-element all-reduce on the same stream (NCCL, a few
+microseconds): when it completes on a rank, every peer's writes into that rank's buffer have completed.  The same
+barriers order buffer reuse: a buffer is written again only after another exchange's barrier, which its owner joins
+only after the kernels that read the buffer.  The buffer that receives the dispatched rows of the forward pass also
+holds them for the backward pass (they are the layer's saved activation), so it rotates over `depth` slots: that
+many forward passes may be in flight before their backward passes.
+
+Requirements: one process per GPU on one node, every rank able to map every other rank's memory (peer access),
+bf16 rows whose length is a multiple of 8.
+"""
+
+from __future__ import annotations
+
+import ctypes
+
+import torch
+import torch.distributed as dist
+
+from . import _lib
+from ._lib import check, lib, stream_ptr
+
+
+class _DeviceMemory:
+    """A raw device allocation presented to torch through the CUDA array interface."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.ptr, self.nbytes = ptr, nbytes
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
+
+
+class PeerBuffer:
+    """`nbytes` of device memory on this rank, and where every rank's buffer of the same name is mapped here."""
+
+    def __init__(self, nbytes: int, group, device: torch.device):
+        self.group, self.device, self.nbytes = group, device, nbytes
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        with torch.cuda.device(device):
+            own = ctypes.c_void_p()
+            check(lib.smoe_peer_alloc(nbytes, ctypes.byref(own)), "peer_alloc")
+            self.own_ptr = own.value
+            handle = (ctypes.c_ubyte * 64)()
+            check(lib.smoe_peer_export(self.own_ptr, handle), "peer_export")
+            handles = [None] * self.world
+            dist.all_gather_object(handles, bytes(handle), group=group)
+            self.ptrs: list[int] = []
+            for r, h in enumerate(handles):
+                if r == self.rank:
+                    self.ptrs.append(self.own_ptr)
+                    continue
+                p = ctypes.c_void_p()
+                raw = (ctypes.c_ubyte * 64).from_buffer_copy(h)
+                check(lib.smoe_peer_open(raw, ctypes.byref(p)), "peer_open")
+                self.ptrs.append(p.value)
+            self.bytes = torch.as_tensor(_DeviceMemory(self.own_ptr, nbytes), device=device)
+
+    def rows(self, n: int, H: int, dtype: torch.dtype) -> torch.Tensor:
+        """The first n rows of this rank's buffer as an (n, H) tensor."""
+        item = torch.empty(0, dtype=dtype).element_size()
+        return self.bytes[: n * H * item].view(dtype).view(n, H)
+
+    def close(self) -> None:
+        """Collective: unmap the peers' buffers, then (after everybody has) free this rank's."""
+        with torch.cuda.device(self.device):
+            torch.cuda.synchronize()
+            for r, p in enumerate(self.ptrs):
+                if r != self.rank:
+                    lib.smoe_peer_close(p)
+            self.ptrs = []
+            dist.barrier(group=self.group)
+            self.bytes = None
+            lib.smoe_peer_free(self.own_ptr)
+            self.own_ptr = None
+
+
+class PeerTransport:
+    """dispatch / combine of token rows over peer memory.  `plan` is an `expert_parallel.DispatchPlan`."""
+
+    def __init__(self, group, device: torch.device, depth: int = 2):
+        self.group, self.device, self.depth = group, device, depth
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        if self.world > lib_max_peers():
+            raise ValueError(f"the peer transport handles at most {lib_max_peers()} ranks")
+        self.buffers: dict[tuple, PeerBuffer] = {}
+        self.flag = torch.zeros(1, dtype=torch.float32, device=device)
+        self.slot = 0
+        self.leased = [False] * depth
+
+    # -- plumbing ------------------------------------------------------------------------------------------
+    def _buffer(self, key: tuple, nbytes: int) -> PeerBuffer:
+        """Every rank asks for the same (key, nbytes) in the same order, so (re)allocation is collective."""
+        buf = self.buffers.get(key)
+        if buf is None or buf.nbytes < nbytes:
+            if buf is not None:
+                buf.close()
+            buf = self.buffers[key] = PeerBuffer(nbytes, self.group, self.device)
+        return buf
+
+    def _barrier(self) -> None:
+        dist.all_reduce(self.flag, group=self.group)
+
+    def close(self) -> None:
+        for buf in self.buffers.values():
+            buf.close()
+        self.buffers = {}
+
+    # -- the two exchanges ---------------------------------------------------------------------------------
+    def dispatch_rows(self, x: torch.Tensor, plan, key: tuple) -> torch.Tensor:
+        """Rows plan.rows.x_gather_idx of x, delivered to their destination ranks; returns the rows this rank
+        received (source by source), a view of the exchange buffer `key`."""
+        _lib.require_cuda(x, "rows")
+        if x.dtype != torch.bfloat16 or x.shape[1] % 8 != 0:
+            raise TypeError("the peer transport moves bf16 rows whose length is a multiple of 8")
+        x = x.contiguous()
+        H = x.shape[1]
+        W = self.world
+        buf = self._buffer(key, W * plan.token_capacity * H * 2)
+        n = plan.rows.x_gather_idx.numel()
+        seg_ptr = (ctypes.c_void_p * W)(*[buf.ptrs[d] + plan.dispatch_offset[d] * H * 2 for d in range(W)])
+        starts = [0]
+        for d in range(W):
+            starts.append(starts[-1] + plan.send_rows[d])
+        seg_start = (ctypes.c_int * (W + 1))(*starts)
+        with torch.cuda.device(self.device):
+            check(lib.smoe_gather_sum_to_peers(x.data_ptr(), None, 0, plan.rows.x_gather_idx.data_ptr(), None, n, H, 1,
+                                               seg_ptr, seg_start, W, stream_ptr(self.device)), "gather_sum_to_peers")
+            self._barrier()
+        return buf.rows(sum(plan.recv_rows), H, x.dtype)
+
+    def return_rows(self, rows: torch.Tensor, plan, key: tuple) -> torch.Tensor:
+        """The inverse exchange: segment s of `rows` (what rank s dispatched here) goes back to rank s; returns this
+        rank's entries in dispatch order (destination-major), a view of the exchange buffer `key`."""
+        _lib.require_cuda(rows, "rows")
+        rows = rows.contiguous()
+        H = rows.shape[1]
+        W = self.world
+        item = rows.element_size()
+        buf = self._buffer(key, W * plan.token_capacity * H * item)
+        with torch.cuda.device(self.device):
+            stream = stream_ptr(self.device)
+            src = rows.data_ptr()
+            for s in range(W):
+                nbytes = plan.recv_rows[s] * H * item
+                check(lib.smoe_peer_copy(buf.ptrs[s] + plan.return_offset[s] * H * item, src, nbytes, stream), "peer_copy")
+                src += nbytes
+            self._barrier()
+        return buf.rows(sum(plan.send_rows), H, rows.dtype)
+
+    # -- slots of the buffer that keeps the forward pass's received rows for the backward pass --------------------
+    def take_slot(self, keep: bool) -> int:
+        slot = self.slot
+        if self.leased[slot]:
+            raise RuntimeError(f"{self.depth} forward passes of the expert-parallel layer are already waiting for their "
+                               "backward pass: construct PeerTransport with a larger depth")
+        self.leased[slot] = keep
+        self.slot = (slot + 1) % self.depth
+        return slot
+
+    def release_slot(self, slot: int) -> None:
+        self.leased[slot] = False
+
+
+def lib_max_peers() -> int:
+    return 16  # SMOE_MAX_PEERS

@@ -47,6 +47,72 @@ class OracleOps:
         return out
 
 
+def _emu_dispatch(x, plan, group=None):
+    """What sonicmoe/peer.py's dispatch does, on CPU: every rank writes its segment for rank d at row
+    plan.dispatch_offset[d] of rank d's buffer (the writes travel through all_gather_object here)."""
+    W, me = dist.get_world_size(group), dist.get_rank(group)
+    segs = x[plan.rows.x_gather_idx.long()].split(plan.send_rows)
+    out = [None] * W
+    dist.all_gather_object(out, [(plan.dispatch_offset[d], segs[d]) for d in range(W)], group=group)
+    buf = torch.full((sum(plan.recv_rows), x.shape[1]), float("nan"), dtype=x.dtype)
+    for s in range(W):
+        off, rows = out[s][me]
+        assert rows.shape[0] == plan.recv_rows[s]
+        buf[off:off + rows.shape[0]] = rows
+    assert not buf.isnan().any()
+    return buf
+
+
+def _emu_return(rows, plan, group=None):
+    W, me = dist.get_world_size(group), dist.get_rank(group)
+    segs = rows.split(plan.recv_rows)
+    out = [None] * W
+    dist.all_gather_object(out, [(plan.return_offset[s], segs[s]) for s in range(W)], group=group)
+    buf = torch.full((sum(plan.send_rows), rows.shape[1]), float("nan"), dtype=rows.dtype)
+    for d in range(W):
+        off, r = out[d][me]
+        assert r.shape[0] == plan.send_rows[d]
+        buf[off:off + r.shape[0]] = r
+    assert not buf.isnan().any()
+    return buf
+
+
+def _emu_sum(entries, plan, T):
+    return torch.zeros(T, entries.shape[1], dtype=entries.dtype).index_add(0, plan.rows.x_gather_idx.long(), entries)
+
+
+class _EmuDispatch(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, plan):
+        ctx.plan, ctx.T = plan, x.shape[0]
+        return _emu_dispatch(x, plan)
+
+    @staticmethod
+    def backward(ctx, g):
+        return _emu_sum(_emu_return(g, ctx.plan), ctx.plan, ctx.T), None
+
+
+class _EmuCombine(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, rows, plan, T):
+        ctx.plan = plan
+        return _emu_sum(_emu_return(rows, plan), plan, T)
+
+    @staticmethod
+    def backward(ctx, g):
+        return _emu_dispatch(g, ctx.plan), None, None
+
+
+class EmulatedPeerTransport:
+    """The peer-memory transport's addressing (segment offsets inside the other ranks' buffers) without GPUs."""
+
+    def dispatch(self, x, plan, keep):
+        return _EmuDispatch.apply(x, plan)
+
+    def combine(self, rows, plan, T):
+        return _EmuCombine.apply(rows, plan, T)
+
+
 def _free_port():
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
@@ -65,7 +131,7 @@ def _logit_bias(E_):
     return 2.0 * torch.log(1.0 / (torch.randperm(E_, generator=g) + 1).float())
 
 
-def _worker(rank, world, port, backend, outdir, use_cuda, use_bias=False):
+def _worker(rank, world, port, backend, outdir, use_cuda, use_bias=False, emulate_peer=False):
     import sys
 
     for p in (ROOT, PKG):
@@ -86,6 +152,8 @@ def _worker(rank, world, port, backend, outdir, use_cuda, use_bias=False):
                                 "c_proj.weight": full["w2"]})
         if not use_cuda:
             m.ops = OracleOps()
+            if emulate_peer:
+                m.transport = EmulatedPeerTransport()
         x = per_rank[rank]["x"].to(dev).requires_grad_(True)
         o, aux = m(x, logit_bias=_logit_bias(E).to(dev) if use_bias else None)
         grads = torch.autograd.grad(o, [x, m.router.weight, m.c_fc.weight, m.c_proj.weight],
@@ -98,13 +166,18 @@ def _worker(rank, world, port, backend, outdir, use_cuda, use_bias=False):
         torch.save({"o": o.detach().float().cpu(), "aux": aux.detach().float().cpu(),
                     "grads": [g.float().cpu() for g in grads]}, os.path.join(outdir, f"rank{rank}.pt"))
         dist.barrier()
+        if use_cuda:
+            from sonicmoe.expert_parallel import close_default_transports
+
+            close_default_transports()
     finally:
         dist.destroy_process_group()
 
 
-def _run_and_check(world, backend, use_cuda, tol, use_bias=False):
+def _run_and_check(world, backend, use_cuda, tol, use_bias=False, emulate_peer=False):
     with tempfile.TemporaryDirectory() as outdir:
-        mp.spawn(_worker, args=(world, _free_port(), backend, outdir, use_cuda, use_bias), nprocs=world, join=True)
+        mp.spawn(_worker, args=(world, _free_port(), backend, outdir, use_cuda, use_bias, emulate_peer), nprocs=world,
+                 join=True)
         res = [torch.load(os.path.join(outdir, f"rank{r}.pt")) for r in range(world)]
     dtype = torch.bfloat16 if use_cuda else torch.float32
     full, per_rank = _inputs(world, dtype)
@@ -201,6 +274,12 @@ def test_expert_parallel_rank_without_rows_gloo(built_library):
     assert (res[1]["grads"][1] == 0).all() and (res[1]["grads"][2] == 0).all()
 
 
+@pytest.mark.parametrize("world", [2, 4])
+def test_peer_transport_addressing_gloo(built_library, world):
+    """Segments written at the plan's offsets into the other ranks' buffers reproduce the all-to-all's result."""
+    _run_and_check(world, "gloo", use_cuda=False, tol=1e-5, emulate_peer=True)
+
+
 def test_expert_parallel_logit_bias_gloo(built_library):
     _run_and_check(2, "gloo", use_cuda=False, tol=1e-5, use_bias=True)
 
@@ -264,7 +343,12 @@ def test_expert_parallel_fp8_ops_single_rank_cuda(built_library, fmt):
 
 
 @pytest.mark.gpu
-def test_expert_parallel_two_ranks_cuda(built_library):
+@pytest.mark.parametrize("transport", ["peer", "nccl"])
+def test_expert_parallel_two_ranks_cuda(built_library, transport, monkeypatch):
+    """Two ranks on two GPUs: rows over peer memory (the library's gather-and-store kernel and copy-engine copies
+    into buffers mapped through CUDA IPC), and over the NCCL all-to-all."""
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
+    monkeypatch.setenv("SONICMOE_EP_TRANSPORT", transport)
+    monkeypatch.setenv("NCCL_NVLS_ENABLE", "0")
     _run_and_check(2, "nccl", use_cuda=True, tol=1e-2)
