@@ -327,6 +327,32 @@ int smoe_mxfp8_up_projection_backward_dx_rows(const void* dzq, const void* dz_sc
                                               void* stream);
 
 /* ---------------------------------------------------------------------------------------------
+ * Fused routing front end
+ * ------------------------------------------------------------------------------------------- */
+
+/* One pass over x (T,H) bf16 with router_w (E,H) bf16: logits (T,E) bf16 = round(x . router_w^T, fp32
+ * accumulation); scores (T,K) fp32 and indices (T,K) int32 as smoe_topk_softmax gives them on those logits;
+ * expert_count (E) int32 = tokens per expert; prob_colsum (E) fp32 = column sums of softmax(logits, dim 1) in fp32
+ * (the mean router probability of the load-balancing loss, before normalisation).  Bit-reproducible.
+ * Stands in for the router linear + sonicmoe::_softmax_topk_fwd + the softmax and column sum of the aux loss
+ * (sonicmoe/functional/__init__.py:438-446, sonicmoe/moe.py:251-274).  Supported when
+ * smoe_router_forward_supported(H, E, K): H % 64 == 0, 32 <= E <= 256, E % 32 == 0, K <= 16.
+ * workspace: smoe_router_forward_workspace_bytes(E) bytes of device memory. */
+int smoe_router_forward_supported(int H, int E, int K);
+size_t smoe_router_forward_workspace_bytes(int E);
+int smoe_router_forward(const void* x, const void* router_w, void* logits, float* scores, int* indices,
+                        int* expert_count, float* prob_colsum, void* workspace, int T, int H, int E, int K,
+                        int* status, void* stream);
+/* dlogits (T,E) bf16, every element written: the sum of g_logits (T,E) bf16 (optional), of the gradient through
+ * the K winners' softmax (dscores, scores (T,K) fp32, indices; optional, as smoe_softmax_topk_backward) and of the
+ * gradient g_colsum (E) fp32 of prob_colsum (optional; the row's softmax is recomputed from logits (T,E) bf16).
+ * Replaces sonicmoe::_softmax_topk_bwd (sonicmoe/functional/backward.py:488-556) plus autograd's softmax backward
+ * of the aux loss. */
+int smoe_router_backward(void* dlogits, const void* logits, const float* dscores, const float* scores,
+                         const int* indices, const float* g_colsum, const void* g_logits, int T, int E, int K,
+                         void* stream);
+
+/* ---------------------------------------------------------------------------------------------
  * Expert parallelism over peer memory (one node, NVLink / NVSwitch).  The reference has no distributed
  * code (sonicmoe/moe.py:260 skips even the aux-loss reduction), so these have no counterpart there; they
  * carry the dispatch / combine exchange of an expert-sharded layer.

@@ -7,6 +7,7 @@ from .count_cumsum import count_cumsum
 from .enums import ActivationType, KernelBackendMoE
 from .functional import enable_quack_gemm, moe_general_routing_inputs, moe_TC_softmax_topk_layer
 from .moe import MoE
+from ._lib import SonicMoEError, check_status
 
 __all__ = [
     "ActivationType",
@@ -16,4 +17,7 @@ __all__ = [
     "enable_quack_gemm",
     "moe_TC_softmax_topk_layer",
     "moe_general_routing_inputs",
+    # beyond the reference's exports: the status check of the bounded-wait GEMM kernels
+    "SonicMoEError",
+    "check_status",
 ]

@@ -79,6 +79,10 @@ SIGNATURES: dict[str, tuple] = {
     "smoe_mxfp8_down_projection_backward_act": (I, [P, P, P, P, P, P, I, P, P, P, P, P, P, I, I, I, I, I, P, P]),
     "smoe_mxfp8_down_projection_backward_act_q": (I, [P, P, P, P, P, P, I, P, P, P, P, P, P, P, P, I, I, I, I, I, P, P]),
     "smoe_mxfp8_up_projection_backward_dx": (I, [P, P, P, P, P, P, I, I, I, I, P, P]),
+    "smoe_router_forward_supported": (I, [I, I, I]),
+    "smoe_router_forward_workspace_bytes": (c_size_t, [I]),
+    "smoe_router_forward": (I, [P, P, P, P, P, P, P, P, I, I, I, I, P, P]),
+    "smoe_router_backward": (I, [P, P, P, P, P, P, P, I, I, I, P]),
     "smoe_peer_alloc": (I, [c_size_t, P]),
     "smoe_peer_free": (I, [P]),
     "smoe_peer_export": (I, [P, P]),
@@ -111,7 +115,7 @@ lib = _load()
 
 
 # kernels one successful entry-point call launches (1 unless listed)
-_KERNELS_PER_CALL = {"route_metadata": 3, "count_cumsum": 2}
+_KERNELS_PER_CALL = {"route_metadata": 3, "count_cumsum": 2, "router_forward": 2}
 _launches = 0
 
 
@@ -155,12 +159,20 @@ class _DeviceState:
     def __init__(self, device: torch.device) -> None:
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
         self.route_ws = torch.empty(0, dtype=torch.int32, device=device)
+        self.router_ws = torch.empty(0, dtype=torch.uint8, device=device)
 
     def route_workspace(self, E: int) -> torch.Tensor:
         need = lib.smoe_route_metadata_workspace_bytes(E) // 4
         if self.route_ws.numel() < need:
             self.route_ws = torch.empty(need, dtype=torch.int32, device=self.status.device)
         return self.route_ws
+
+
+    def router_workspace(self, E: int) -> torch.Tensor:
+        need = lib.smoe_router_forward_workspace_bytes(E)
+        if self.router_ws.numel() < need:
+            self.router_ws = torch.empty(need, dtype=torch.uint8, device=self.status.device)
+        return self.router_ws
 
 
 _states: dict[int, _DeviceState] = {}

@@ -41,6 +41,8 @@ __all__ = [
     "forward_token_choice_rounding",
     "topk_softmax",
     "set_fused_combine",
+    "set_fused_router",
+    "layer_router_logits",
 ]
 
 
@@ -204,6 +206,89 @@ class _TopkSoftmax(torch.autograd.Function):
 
 def topk_softmax(router_logits: torch.Tensor, K: int) -> tuple[torch.Tensor, torch.Tensor]:
     return _TopkSoftmax.apply(router_logits, K)
+
+
+# ------------------------------------------------------------------------------------------------
+# fused routing front end
+# ------------------------------------------------------------------------------------------------
+_FUSED_ROUTER = os.getenv("SONICMOE_FUSED_ROUTER", "1") != "0"
+
+
+def set_fused_router(enable: bool) -> bool:
+    """Use the one-pass router kernel where it applies (default) or always the separate router linear + top-k;
+    returns the previous setting."""
+    global _FUSED_ROUTER
+    prev, _FUSED_ROUTER = _FUSED_ROUTER, bool(enable)
+    return prev
+
+
+def fused_router_applies(x: torch.Tensor, router_w: torch.Tensor, K: int) -> bool:
+    return (_FUSED_ROUTER and x.is_cuda and x.dtype == torch.bfloat16 and router_w.dtype == torch.bfloat16
+            and not torch.compiler.is_compiling()
+            and bool(lib.smoe_router_forward_supported(x.shape[1], router_w.shape[0], K)))
+
+
+@torch.no_grad()
+def layer_router_logits(x: torch.Tensor, router_w: torch.Tensor, K: int) -> torch.Tensor:
+    """The router logits exactly as `moe_TC_softmax_topk_layer` computes them for these inputs (the fused kernel's
+    where it applies, the router linear's otherwise) -- what a check of the routing decision must be run on."""
+    if fused_router_applies(x, router_w, K):
+        return _FusedRouter.apply(x, router_w, K)[0]
+    return F.linear(x if x.dtype == router_w.dtype else x.to(router_w.dtype), router_w)
+
+
+class _FusedRouter(torch.autograd.Function):
+    """(logits (T,E) bf16, scores (T,K) fp32, indices (T,K) int32, expert_frequency (E) int32, prob_colsum (E) fp32)
+    from one pass over x: router GEMM, top-K + softmax over the winners, token counts and the column sums of the
+    full softmax, in one kernel.  Routing is decided on the bf16 logits this returns.  Backward: one kernel turns
+    the gradients of logits, scores and prob_colsum into dlogits; the two router GEMMs stay library calls, as the
+    forward one does in the reference (sonicmoe/functional/__init__.py:438-446, sonicmoe/moe.py:251-274)."""
+
+    @staticmethod
+    def forward(ctx, x, router_w, K: int):
+        x = x.contiguous()
+        router_w = router_w.contiguous()
+        T, H = x.shape
+        E = router_w.shape[0]
+        dev = x.device
+        st = _lib.device_state(dev)
+        with torch.cuda.device(dev):
+            logits = torch.empty(T, E, dtype=torch.bfloat16, device=dev)
+            scores = torch.empty(T, K, dtype=torch.float32, device=dev)
+            indices = torch.empty(T, K, dtype=torch.int32, device=dev)
+            freq = torch.empty(E, dtype=torch.int32, device=dev)
+            colsum = torch.empty(E, dtype=torch.float32, device=dev)
+            ws = st.router_workspace(E)
+            check(lib.smoe_router_forward(x.data_ptr(), router_w.data_ptr(), logits.data_ptr(), scores.data_ptr(),
+                                          indices.data_ptr(), freq.data_ptr(), colsum.data_ptr(), ws.data_ptr(),
+                                          T, H, E, K, st.status.data_ptr(), stream_ptr(dev)), "router_forward")
+        ctx.save_for_backward(x, router_w, logits, scores, indices)
+        ctx.mark_non_differentiable(indices, freq)
+        ctx.set_materialize_grads(False)
+        return logits, scores, indices, freq, colsum
+
+    @staticmethod
+    def backward(ctx, g_logits, g_scores, _gi, _gf, g_colsum):
+        x, router_w, logits, scores, indices = ctx.saved_tensors
+        if g_logits is None and g_scores is None and g_colsum is None:
+            return None, None, None
+        T, E = logits.shape
+        K = scores.shape[1]
+        dev = x.device
+        if g_logits is not None:
+            g_logits = g_logits.contiguous().to(torch.bfloat16)
+        if g_scores is not None:
+            g_scores = g_scores.contiguous().float()
+        if g_colsum is not None:
+            g_colsum = g_colsum.contiguous().float()
+        with torch.cuda.device(dev):
+            dlogits = torch.empty_like(logits)
+            check(lib.smoe_router_backward(dlogits.data_ptr(), logits.data_ptr(), ptr(g_scores), scores.data_ptr(),
+                                           indices.data_ptr(), ptr(g_colsum), ptr(g_logits), T, E, K,
+                                           stream_ptr(dev)), "router_backward")
+        dx = dlogits @ router_w if ctx.needs_input_grad[0] else None
+        dw = dlogits.t() @ x if ctx.needs_input_grad[1] else None
+        return dx, dw, None
 
 
 # ------------------------------------------------------------------------------------------------
@@ -484,22 +569,36 @@ def moe_TC_softmax_topk_layer(
     (E,2I,H) / (E,H,I) parameters, gate/up rows of w1 interleaved.
     Reference: sonicmoe/functional/__init__.py:423-490.
     """
+    o, router_logits, freq, _ = moe_TC_softmax_topk_layer_with_router_stats(
+        x, router_w, w1, b1, w2, b2, K, stream_id, activation_type, is_inference_mode_enabled)
+    return o, router_logits, freq
+
+
+def moe_TC_softmax_topk_layer_with_router_stats(x, router_w, w1, b1, w2, b2, K, stream_id=0,
+                                                activation_type=ActivationType.SWIGLU,
+                                                is_inference_mode_enabled=False):
+    """`moe_TC_softmax_topk_layer` plus a fourth result: the column sums (E,) fp32 of softmax(router_logits) when the
+    fused routing kernel produced them (what the load-balancing loss needs), else None."""
     activation_type = _check_experts_args(x, w1, w2, b1, b2, activation_type)
     E = router_w.size(0)
     T = x.size(0)
-    # a router kept in fp32 (an extension over the reference) computes its logits in fp32
-    router_logits = F.linear(x if x.dtype == router_w.dtype else x.to(router_w.dtype), router_w)
     inference = is_inference_mode_enabled or not torch.is_grad_enabled()
-    if torch.compiler.is_compiling() and b1 is None and activation_type == ActivationType.SWIGLU:
-        # opaque custom ops instead of autograd functions with ctypes calls inside (torch.compile, fullgraph)
-        from .compiled_ops import layer_with_custom_ops
+    if fused_router_applies(x, router_w, K):
+        router_logits, scores, indices, _freq, colsum = _FusedRouter.apply(x, router_w, K)
+    else:
+        colsum = None
+        # a router kept in fp32 (an extension over the reference) computes its logits in fp32
+        router_logits = F.linear(x if x.dtype == router_w.dtype else x.to(router_w.dtype), router_w)
+        if torch.compiler.is_compiling() and b1 is None and activation_type == ActivationType.SWIGLU:
+            # opaque custom ops instead of autograd functions with ctypes calls inside (torch.compile, fullgraph)
+            from .compiled_ops import layer_with_custom_ops
 
-        o, freq = layer_with_custom_ops(x, router_logits, w1, w2, K, E, inference)
-        return o, router_logits, freq
-    scores, indices = topk_softmax(router_logits, K)
+            o, freq = layer_with_custom_ops(x, router_logits, w1, w2, K, E, inference)
+            return o, router_logits, freq, None
+        scores, indices = topk_softmax(router_logits, K)
     route = _route_metadata(indices.reshape(-1), None, E, K)
     o = _experts(x, w1, b1, w2, b2, scores.reshape(-1), route, T, inference, activation_type)
-    return o, router_logits, route.expert_frequency
+    return o, router_logits, route.expert_frequency, colsum
 
 
 def moe_general_routing_inputs(

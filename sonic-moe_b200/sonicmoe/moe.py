@@ -14,7 +14,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from .enums import ActivationType, KernelBackendMoE, is_glu
-from .functional import moe_TC_softmax_topk_layer
+from .functional import moe_TC_softmax_topk_layer, moe_TC_softmax_topk_layer_with_router_stats
 
 
 def _glu_halves(z: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
@@ -112,8 +112,9 @@ class MoE(nn.Module):
         original_shape = hidden_states.shape
         hidden_states = hidden_states.view(-1, self.hidden_size)
 
+        prob_colsum = None
         if kernel_backend_moe == KernelBackendMoE.sonicmoe:
-            out, router_logits, expert_frequency = moe_TC_softmax_topk_layer(
+            out, router_logits, expert_frequency, prob_colsum = moe_TC_softmax_topk_layer_with_router_stats(
                 hidden_states,
                 self.router.weight,
                 self.c_fc.weight.permute(1, 2, 0),
@@ -131,11 +132,16 @@ class MoE(nn.Module):
             raise ValueError(f"kernel backend {kernel_backend_moe} is not provided by this build")
 
         out = out.view(original_shape)
-        aux_loss = self._compute_switch_loss(
-            logits=router_logits,
-            probs=F.softmax(router_logits, dim=-1, dtype=torch.float32),
-            expert_frequency=expert_frequency,
-        )
+        if prob_colsum is not None:
+            # the fused routing kernel already summed softmax(router_logits) over the tokens
+            share = F.normalize(expert_frequency.float(), p=1, dim=0)
+            aux_loss = self.num_experts * (F.normalize(prob_colsum, p=1, dim=0) * share).sum()
+        else:
+            aux_loss = self._compute_switch_loss(
+                logits=router_logits,
+                probs=F.softmax(router_logits, dim=-1, dtype=torch.float32),
+                expert_frequency=expert_frequency,
+            )
         return out, aux_loss
 
     def _compute_switch_loss(self, logits: torch.Tensor, probs: torch.Tensor,

@@ -66,7 +66,7 @@ def test_module_forward_backward_vs_oracle(built_library, T, H, I, E, K, fused_c
     torch.cuda.synchronize()
     _lib.check_status()
 
-    logits = torch.nn.functional.linear(x.detach(), m.router.weight.detach())
+    logits = functional.layer_router_logits(x.detach(), m.router.weight.detach(), K)
     f32 = {k: v.float() for k, v in inp.items()}
     ref = orc.moe_layer(f32["x"], f32["router_w"], f32["w1"], f32["w2"], K, dout=f32["dout"],
                         logits=logits.float().cpu())
@@ -259,7 +259,9 @@ def test_bias_and_activations_vs_oracle(built_library, act, bias):
     torch.cuda.synchronize()
     _lib.check_status()
 
-    logits = torch.nn.functional.linear(x.detach(), m.router.weight.detach()).float().cpu()
+    from sonicmoe.functional import layer_router_logits
+
+    logits = layer_router_logits(x.detach(), m.router.weight.detach(), K).float().cpu()
     scores, idx = orc.topk_softmax(logits, K)
     route = orc.route_metadata(idx, E, T, K=K)
     f = lambda t: None if t is None else t.detach().float().cpu()
