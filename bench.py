@@ -222,7 +222,7 @@ def time_kernels(moe, x, dout, cfg, peaks, reps=5):
     st = _lib.device_state(dev).status.data_ptr()
     stream = torch.cuda.current_stream().cuda_stream
     with torch.no_grad():
-        logits = torch.nn.functional.linear(x, moe.router.weight)
+        logits = torch.nn.functional.linear(x, moe.router.weight).contiguous()
         scores, idx = fn.topk_softmax(logits, K)
         route = fn._route_metadata(idx.reshape(-1), None, E, K)
     off, gat, sct, rev = (route.expert_frequency_offset.data_ptr(), route.x_gather_idx.data_ptr(),
@@ -258,6 +258,31 @@ def time_kernels(moe, x, dout, cfg, peaks, reps=5):
         "gather_sum_plain": (gather_bytes, lambda: lib.smoe_gather_sum(
             y2.data_ptr(), o.data_ptr(), None, 0, rev, None, T, H, K, stream)),
     }
+    # routing kernels (HBM / latency bound): the fused front end, the counting sort, the router backward kernel
+    rw = moe.router.weight.detach()
+    if lib.smoe_router_forward_supported(H, E, K):
+        r_logits = torch.empty(T, E, **bf)
+        r_scores = torch.empty(T, K, dtype=torch.float32, device=dev)
+        r_idx = torch.empty(T, K, dtype=torch.int32, device=dev)
+        r_cnt = torch.empty(E, dtype=torch.int32, device=dev)
+        r_col = torch.empty(E, dtype=torch.float32, device=dev)
+        r_ws = _lib.device_state(dev).router_workspace(E)
+        hbm_ops["router_forward_fused"] = (T * H * 2 + E * H * 2 + T * E * 2 + T * K * 8, lambda: lib.smoe_router_forward(
+            x.data_ptr(), rw.data_ptr(), r_logits.data_ptr(), r_scores.data_ptr(), r_idx.data_ptr(), r_cnt.data_ptr(),
+            r_col.data_ptr(), r_ws.data_ptr(), T, H, E, K, st, stream))
+        g_sc = torch.randn(T, K, device=dev)
+        d_logits = torch.empty(T, E, **bf)
+        hbm_ops["router_backward"] = (2 * T * E * 2 + T * K * 12, lambda: lib.smoe_router_backward(
+            d_logits.data_ptr(), logits.data_ptr(), g_sc.data_ptr(), sc.data_ptr(), idx.data_ptr(), None, None, T, E, K,
+            stream))
+    m_ws = _lib.device_state(dev).route_workspace(E)
+    m_out = torch.empty(3, TK, dtype=torch.int32, device=dev)
+    m_cnt = torch.empty(E, dtype=torch.int32, device=dev)
+    m_off = torch.empty(E + 1, dtype=torch.int32, device=dev)
+    idx_flat = idx.reshape(-1).contiguous()
+    hbm_ops["route_metadata"] = (TK * 4 + 3 * TK * 4, lambda: lib.smoe_route_metadata(
+        idx_flat.data_ptr(), None, TK, E, K, m_cnt.data_ptr(), m_off.data_ptr(), m_out[0].data_ptr(),
+        m_out[1].data_ptr(), m_out[2].data_ptr(), m_ws.data_ptr(), stream))
     out = {}
 
     def timed(fn_):
@@ -295,6 +320,70 @@ NCU_TRAFFIC_BYTES = {  # profiles/grouped_gemm_pair_T8192_E32_ncu_full.txt, scal
     "up_projection_weight_grad": 4.50e9,
     "up_projection_backward_dx": 5.28e9,
 }
+
+
+def profile_step(args, local_rank):
+    """Where one steady-state step's time goes: every kernel's device time inside the step (CUPTI through
+    torch.profiler), their sum, and the part of the step during which no kernel ran (launch gaps / host stalls).
+    Prints one JSON object; not a benchmark number (profiling slows the host side down)."""
+    from torch.profiler import ProfilerActivity, profile
+
+    cfg = CFG
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    T, H = cfg["T"], cfg["H"]
+    moe = build_layer(cfg, dev)
+    g = torch.Generator(device=dev).manual_seed(1234)
+    x = torch.randn(T, H, generator=g, device=dev).bfloat16().requires_grad_(True)
+    dout = torch.randn(T, H, generator=g, device=dev).bfloat16()
+
+    def step():
+        zero_grads(moe, x)
+        o, _aux = moe(x)
+        o.backward(dout)
+
+    for _ in range(5):
+        step()
+    torch.cuda.synchronize()
+    n = 5
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        e0.record()
+        for _ in range(n):
+            step()
+        e1.record()
+        torch.cuda.synchronize()
+    step_ms = e0.elapsed_time(e1) / n
+    spans = []
+    per_kernel = {}
+    for ev in prof.events():
+        if ev.device_type.name != "CUDA":
+            continue
+        dur_us = ev.time_range.end - ev.time_range.start
+        if dur_us <= 0:
+            continue
+        spans.append((ev.time_range.start, ev.time_range.end))
+        name = ev.name.split("<")[0].split("(")[0][-60:]
+        k = per_kernel.setdefault(name, [0, 0.0])
+        k[0] += 1
+        k[1] += dur_us
+    spans.sort()
+    busy = 0.0
+    cur_s, cur_e = spans[0]
+    for s_, e_ in spans[1:]:
+        if s_ <= cur_e:
+            cur_e = max(cur_e, e_)
+        else:
+            busy += cur_e - cur_s
+            cur_s, cur_e = s_, e_
+    busy += cur_e - cur_s
+    kernels = sorted(((v[1] / n / 1e3, v[0] // n, k) for k, v in per_kernel.items()), reverse=True)
+    print(json.dumps({
+        "step_ms_cuda_events": step_ms, "kernel_busy_ms_per_step": busy / n / 1e3,
+        "idle_ms_per_step": step_ms - busy / n / 1e3,
+        "kernel_ms_sum_per_step": sum(k[0] for k in kernels), "launches_per_step": sum(k[1] for k in kernels),
+        "kernels": [{"ms_per_step": round(ms, 4), "launches_per_step": cnt, "name": name} for ms, cnt, name in kernels],
+    }), flush=True)
 
 
 def run_gpu_arm(args, rank, world, local_rank):
@@ -881,6 +970,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     # profiling aid: time (or let ncu capture) each kernel alone on a reduced token / expert count
     ap.add_argument("--kernels-only", action="store_true")
+    # profiling aid: per-kernel device time and idle time inside a steady-state step (torch.profiler)
+    ap.add_argument("--profile-step", action="store_true")
     ap.add_argument("--tokens", type=int, default=CFG["T"])
     ap.add_argument("--experts", type=int, default=CFG["E"])
     ap.add_argument("--reps", type=int, default=5)
@@ -896,6 +987,9 @@ def main():
         return
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the layer has no CPU path (use --impl reference for the CPU arm)")
+    if args.profile_step:
+        profile_step(args, local_rank)
+        return
     if args.workload == "token_rounding":
         run_rounding_arm(args, local_rank)
         return

@@ -446,6 +446,63 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     for (long long t = first_tile; ok && decode_tile<RAGGED_K, DUAL>(p, ss, t, num_n, rank, tile); t += tile_step) {
       const bool have_acc = tile.num_kb > 0;
       constexpr int SUBTILES = DUAL == DUAL_NONE ? 1 : 2;
+      if constexpr (DUAL != DUAL_NONE && EPI == EPI_STORE) {
+        // Plain stores: both accumulators are copied out, rounded to bf16 (two values per register, 64 registers
+        // per accumulator) and handed back before anything is stored, so the next unit's MMAs wait for two
+        // tensor-memory reads and not for this unit's stores.
+        constexpr int CHUNKS = COLS_PER_WARP / 32;  // 4
+        static_assert(COLS_PER_WARP == 128, "dual tiles use 8 epilogue warps");
+        uint32_t packed[2][CHUNKS * 16];
+#pragma unroll
+        for (int sub = 0; sub < 2; ++sub) {
+          if (have_acc) {
+            if (!mbar_wait(smem_u32(&ss.acc_full[sub]), acc_phase, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t t_addr = tmem_base + sub * BN + (static_cast<uint32_t>(quad * 32) << 16);
+#pragma unroll
+            for (int h = 0; h < CHUNKS / 2; ++h) {
+              uint32_t v0[32], v1[32];
+              tmem_ld32(t_addr + (col_half * CHUNKS + 2 * h) * 32, v0);
+              tmem_ld32(t_addr + (col_half * CHUNKS + 2 * h + 1) * 32, v1);
+              tmem_ld_wait();
+              if (h == CHUNKS / 2 - 1) {  // last read of this accumulator: give it back before converting
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster_relaxed(map_to_cta(smem_u32(&ss.acc_empty[sub]), 0));
+              }
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                packed[sub][(2 * h) * 16 + j] = pack_bf16(__uint_as_float(v0[2 * j]), __uint_as_float(v0[2 * j + 1]));
+                packed[sub][(2 * h + 1) * 16 + j] = pack_bf16(__uint_as_float(v1[2 * j]), __uint_as_float(v1[2 * j + 1]));
+              }
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < CHUNKS * 16; ++j) packed[sub][j] = 0u;
+          }
+        }
+        if (!ok) break;
+#pragma unroll
+        for (int sub = 0; sub < 2; ++sub) {
+          const int r = tile.row0 + (DUAL == DUAL_M ? sub * 2 * BM : 0) + row_in_tile;
+          const int n0 = tile.n0 + (DUAL == DUAL_N ? sub * BN : 0);
+          if (r < tile.row_end) {
+            __nv_bfloat16* dst = p.out0 + (RAGGED_K ? tile.e * p.out0_expert_stride : 0ll) + r * p.ld0;
+#pragma unroll
+            for (int c = 0; c < CHUNKS; ++c) {
+              const int n = n0 + (col_half * CHUNKS + c) * 32;
+              if (n < p.N) {
+#pragma unroll
+                for (int q = 0; q < 4; ++q)
+                  reinterpret_cast<uint4*>(dst + n)[q] = make_uint4(packed[sub][c * 16 + 4 * q], packed[sub][c * 16 + 4 * q + 1],
+                                                                    packed[sub][c * 16 + 4 * q + 2], packed[sub][c * 16 + 4 * q + 3]);
+              }
+            }
+          }
+        }
+        if (have_acc) acc_phase ^= 1u;
+        continue;
+      }
 #pragma unroll 1
       for (int sub = 0; sub < SUBTILES && ok; ++sub) {
         if constexpr (DUAL != DUAL_NONE) acc = sub;
@@ -456,6 +513,15 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         if constexpr (EPI == EPI_DSWIGLU || EPI == EPI_DACT || EPI == EPI_SCATTER || EPI == EPI_STORE_ROWS) {
           if (row_ok && (EPI != EPI_STORE_ROWS || p.scores != nullptr))
             score = load_score(p.scores, p.scores_are_bf16, p.s_scatter[r]);
+        }
+        if constexpr (EPI == EPI_DSWIGLU || EPI == EPI_DACT) {
+          // the epilogue reads this thread's piece of the saved pre-activation row: have the L2 fetch it while the
+          // unit's MMAs are still running
+          if (row_ok && n0 + col_half * COLS_PER_WARP < p.N) {
+            const int zw = (EPI == EPI_DACT && !act_is_gated(p.act)) ? 1 : 2;  // z columns per accumulator column
+            prefetch_l2_lines(p.z + static_cast<long long>(r) * (zw * p.N) + zw * (n0 + col_half * COLS_PER_WARP),
+                              zw * COLS_PER_WARP * 2 / 128);
+          }
         }
         if (have_acc) {
           if (!mbar_wait(smem_u32(&ss.acc_full[acc]), acc_phase, abort_flag)) { ok = false; break; }
