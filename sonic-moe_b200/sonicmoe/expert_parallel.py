@@ -55,6 +55,12 @@ def record_exchanges(enable: bool) -> list | None:
     being filled (pairs of events; read them after a synchronize)."""
     global _exchange_events
     prev, _exchange_events = _exchange_events, ([] if enable else None)
+    try:
+        from . import peer
+
+        peer.exchange_events = _exchange_events
+    except ImportError:  # no library on this machine: only the collective transport exists
+        pass
     return prev
 
 
@@ -120,53 +126,72 @@ class DispatchPlan:
     token_capacity: int           # most tokens any rank holds: a rank receives at most world_size * this many rows
 
 
-def plan_dispatch(indices: torch.Tensor, num_experts: int, world_size: int, group) -> DispatchPlan:
-    """indices (T, K): global expert of every (token, k) slot.  One device->host read (the split sizes)."""
+def _chunk_routing(indices: torch.Tensor, e_local: int, world_size: int):
+    """Device-side part of one chunk's plan that does not need the split sizes."""
     T, K = indices.shape
     dev = indices.device
-    e_local = num_experts // world_size
     idx = indices.long()
     dest = idx // e_local                                                   # (T, K)
     to_rank = torch.zeros(T, world_size, dtype=torch.bool, device=dev).scatter_(1, dest, True)
     by_rank = to_rank.t().contiguous()                                      # (W, T)
     row_counts = by_rank.sum(1)
     pair_counts = torch.bincount(dest.reshape(-1), minlength=world_size)
-    # every rank learns every rank's counts (and token count): rows[s][d], pairs[s][d] from rank s to rank d
-    mine = torch.cat([row_counts, pair_counts, row_counts.new_tensor([T])]).to(torch.int32)
-    everyone = torch.empty(world_size * (2 * world_size + 1), dtype=torch.int32, device=dev)
-    dist.all_gather_into_tensor(everyone, mine, group=group)
-    host = everyone.view(world_size, 2 * world_size + 1).cpu().tolist()                                          # the layer's one host synchronisation
-    me = dist.get_rank(group)
+    counts = torch.cat([row_counts, pair_counts, row_counts.new_tensor([T])]).to(torch.int32)
+    return idx, dest, to_rank, by_rank, counts
+
+
+def plan_dispatch(indices: torch.Tensor, num_experts: int, world_size: int, group,
+                  bounds: list[int] | None = None) -> list[DispatchPlan]:
+    """indices (T, K): global expert of every (token, k) slot.  One plan per chunk of tokens
+    [bounds[c], bounds[c+1]) (default: one chunk, all tokens); all chunks share ONE exchange of counts and one
+    device->host read (the split sizes)."""
+    T, K = indices.shape
+    dev = indices.device
     W = world_size
-    rows_sd = [h[:W] for h in host]
-    pairs_sd = [h[W:2 * W] for h in host]
-    send_rows, send_pairs = rows_sd[me], pairs_sd[me]
-    recv_rows = [rows_sd[s][me] for s in range(W)]
-    recv_pairs = [pairs_sd[s][me] for s in range(W)]
-    dispatch_offset = [sum(rows_sd[s][d] for s in range(me)) for d in range(W)]
-    return_offset = [sum(rows_sd[s][d] for d in range(me)) for s in range(W)]
-    token_capacity = max(h[2 * W] for h in host)
-    n = sum(send_rows)
+    e_local = num_experts // W
+    bounds = bounds or [0, T]
+    chunks = len(bounds) - 1
+    parts = [_chunk_routing(indices[bounds[c]:bounds[c + 1]], e_local, W) for c in range(chunks)]
+    # every rank learns every rank's counts (and token count): rows[s][d], pairs[s][d] from rank s to rank d
+    width = chunks * (2 * W + 1)
+    mine = torch.cat([p[4] for p in parts])
+    everyone = torch.empty(W * width, dtype=torch.int32, device=dev)
+    dist.all_gather_into_tensor(everyone, mine, group=group)
+    host = everyone.view(W, chunks, 2 * W + 1).cpu().tolist()               # the layer's one host synchronisation
+    me = dist.get_rank(group)
+    plans = []
+    for c, (idx, dest, to_rank, by_rank, _) in enumerate(parts):
+        Tc = bounds[c + 1] - bounds[c]
+        rows_sd = [host[s][c][:W] for s in range(W)]
+        pairs_sd = [host[s][c][W:2 * W] for s in range(W)]
+        send_rows, send_pairs = rows_sd[me], pairs_sd[me]
+        recv_rows = [rows_sd[s][me] for s in range(W)]
+        recv_pairs = [pairs_sd[s][me] for s in range(W)]
+        dispatch_offset = [sum(rows_sd[s][d] for s in range(me)) for d in range(W)]
+        return_offset = [sum(rows_sd[s][d] for d in range(me)) for s in range(W)]
+        token_capacity = max(host[s][c][2 * W] for s in range(W))
+        n = sum(send_rows)
 
-    # entries: positions of the set bits of by_rank in row-major order = destination-major, tokens ascending
-    flat = by_rank.reshape(-1)
-    entry = torch.argsort((~flat).to(torch.uint8), stable=True)[:n]
-    entry_token = (entry % T).to(torch.int32)
-    rev = torch.argsort(entry_token, stable=True).to(torch.int32)
-    per_token = to_rank.sum(1)
-    offset = torch.zeros(T + 1, dtype=torch.int32, device=dev)
-    offset[1:] = per_token.cumsum(0)
-    rows = RowList(entry_token, rev, offset)
+        # entries: positions of the set bits of by_rank in row-major order = destination-major, tokens ascending
+        flat = by_rank.reshape(-1)
+        entry = torch.argsort((~flat).to(torch.uint8), stable=True)[:n]
+        entry_token = (entry % max(Tc, 1)).to(torch.int32)
+        rev = torch.argsort(entry_token, stable=True).to(torch.int32)
+        per_token = to_rank.sum(1)
+        offset = torch.zeros(Tc + 1, dtype=torch.int32, device=dev)
+        offset[1:] = per_token.cumsum(0)
+        rows = RowList(entry_token, rev, offset)
 
-    # pairs ordered by (destination, token): the order in which the destination lists them by received row
-    flat_dest = dest.reshape(-1)
-    token_of_slot = torch.arange(T, device=dev).repeat_interleave(K)
-    pair_slot = torch.argsort(flat_dest * T + token_of_slot, stable=True)
-    rank_in_segment = by_rank.long().cumsum(1) - 1                          # (W, T) position of token t in segment d
-    pair_row = rank_in_segment[flat_dest[pair_slot], token_of_slot[pair_slot]].to(torch.int32)
-    pair_expert = (idx.reshape(-1)[pair_slot] % e_local).to(torch.int32)
-    return DispatchPlan(rows, pair_slot, pair_row, pair_expert, send_rows, recv_rows, send_pairs, recv_pairs,
-                        dispatch_offset, return_offset, token_capacity)
+        # pairs ordered by (destination, token): the order in which the destination lists them by received row
+        flat_dest = dest.reshape(-1)
+        token_of_slot = torch.arange(Tc, device=dev).repeat_interleave(K)
+        pair_slot = torch.argsort(flat_dest * max(Tc, 1) + token_of_slot, stable=True)
+        rank_in_segment = by_rank.long().cumsum(1) - 1                      # (W, Tc) position of token t in segment d
+        pair_row = rank_in_segment[flat_dest[pair_slot], token_of_slot[pair_slot]].to(torch.int32)
+        pair_expert = (idx.reshape(-1)[pair_slot] % e_local).to(torch.int32)
+        plans.append(DispatchPlan(rows, pair_slot, pair_row, pair_expert, send_rows, recv_rows, send_pairs,
+                                  recv_pairs, dispatch_offset, return_offset, token_capacity))
+    return plans
 
 
 def received_pair_tokens(pair_row: torch.Tensor, recv_rows: list[int], recv_pairs: list[int]) -> torch.Tensor:
@@ -278,18 +303,31 @@ def _sum_rows(entries, rows, T):
     return out
 
 
+# A transport moves token rows between the ranks in two steps each way, so that a caller can keep several chunks of
+# tokens in flight:  h = dispatch_start(x, plan, keep, tag); x_recv = dispatch_wait(h)  and
+# h = combine_start(rows, plan, tag); o = combine_finish(h, plan, T).  `micro_batches` is how many chunks it
+# wants the layer to cut the tokens into (1 = no pipelining).
+
+
 class CollectiveTransport:
     """Token rows by `all_to_all_single` of the process group's backend (NCCL on GPUs, gloo in the CPU tests)."""
 
-    def __init__(self, group, ops):
-        self.group, self.ops = group, ops
+    micro_batches = 1
 
-    def dispatch(self, x, plan, keep):
+    def __init__(self, group, ops, micro_batches: int = 1):
+        self.group, self.ops, self.micro_batches = group, ops, micro_batches
+
+    def dispatch_start(self, x, plan, keep, tag):
         return _AllToAllRows.apply(self.ops.gather_rows(x, plan.rows), plan.send_rows, plan.recv_rows, self.group)
 
-    def combine(self, rows, plan, T):
-        back = _AllToAllRows.apply(rows, plan.recv_rows, plan.send_rows, self.group)
-        return self.ops.sum_rows(back, plan.rows, T)
+    def dispatch_wait(self, handle):
+        return handle
+
+    def combine_start(self, rows, plan, tag):
+        return _AllToAllRows.apply(rows, plan.recv_rows, plan.send_rows, self.group)
+
+    def combine_finish(self, handle, plan, T):
+        return self.ops.sum_rows(handle, plan.rows, T)
 
 
 class _Lease:
@@ -307,18 +345,17 @@ class _PeerDispatch(torch.autograd.Function):
     buffer (gather fused with the send); backward: the row gradients go back and each token's are added up."""
 
     @staticmethod
-    def forward(ctx, x, plan, transport, keep):
-        slot = transport.take_slot(keep)
+    def forward(ctx, x, plan, transport, keep, slot, tag):
         if keep:
             ctx.lease = _Lease(transport, slot)
-        ctx.plan, ctx.transport, ctx.T = plan, transport, x.shape[0]
-        return _timed_exchange(lambda: transport.dispatch_rows(x, plan, ("dispatch_fwd", slot)), True)
+        ctx.plan, ctx.transport, ctx.T, ctx.tag = plan, transport, x.shape[0], tag
+        return _timed_exchange(lambda: transport.dispatch_rows(x, plan, ("dispatch_fwd", slot, tag)), True)
 
     @staticmethod
     def backward(ctx, g):
-        back = _timed_exchange(lambda: ctx.transport.return_rows(g, ctx.plan, ("return_bwd",)), True)
+        back = _timed_exchange(lambda: ctx.transport.return_rows(g, ctx.plan, ("return_bwd", ctx.tag)), True)
         ctx.lease = None
-        return _sum_rows(back, ctx.plan.rows, ctx.T), None, None, None
+        return _sum_rows(back, ctx.plan.rows, ctx.T), None, None, None, None, None
 
 
 class _PeerCombine(torch.autograd.Function):
@@ -326,30 +363,184 @@ class _PeerCombine(torch.autograd.Function):
     gradient's rows dispatched to the expert ranks (the same fused gather + send)."""
 
     @staticmethod
-    def forward(ctx, rows, plan, transport, T):
-        ctx.plan, ctx.transport = plan, transport
-        back = _timed_exchange(lambda: transport.return_rows(rows, plan, ("return_fwd",)), True)
+    def forward(ctx, rows, plan, transport, T, tag):
+        ctx.plan, ctx.transport, ctx.tag = plan, transport, tag
+        back = _timed_exchange(lambda: transport.return_rows(rows, plan, ("return_fwd", tag)), True)
         return _sum_rows(back, plan.rows, T)
 
     @staticmethod
     def backward(ctx, g):
-        return _timed_exchange(lambda: ctx.transport.dispatch_rows(g, ctx.plan, ("dispatch_bwd",)), True), None, None, None
+        return (_timed_exchange(lambda: ctx.transport.dispatch_rows(g, ctx.plan, ("dispatch_bwd", ctx.tag)), True),
+                None, None, None, None)
 
 
 class PeerMemoryTransport:
     """Token rows through buffers the ranks map from each other (sonicmoe/peer.py): the library's own kernels and
-    copy-engine copies over NVLink instead of an NCCL all-to-all.  bf16 CUDA rows, one node."""
+    copy-engine copies over NVLink instead of an NCCL all-to-all, every exchange in order on the caller's stream.
+    bf16 CUDA rows, one node."""
+
+    micro_batches = 1
 
     def __init__(self, group, device, depth: int = 2):
         from .peer import PeerTransport
 
         self.impl = PeerTransport(group, device, depth)
 
-    def dispatch(self, x, plan, keep):
-        return _PeerDispatch.apply(x, plan, self.impl, keep)
+    def dispatch_start(self, x, plan, keep, tag):
+        if tag == 0:
+            self._slot = self.impl.take_slot(keep)
+        return _PeerDispatch.apply(x, plan, self.impl, keep and tag == 0, self._slot, tag)
 
-    def combine(self, rows, plan, T):
-        return _PeerCombine.apply(rows, plan, self.impl, T)
+    def dispatch_wait(self, handle):
+        return handle
+
+    def combine_start(self, rows, plan, tag):
+        return (rows, tag)
+
+    def combine_finish(self, handle, plan, T):
+        rows, tag = handle
+        return _PeerCombine.apply(rows, plan, self.impl, T, tag)
+
+    def close(self):
+        self.impl.close()
+
+
+class _Flight:
+    """What the autograd nodes of one chunk's exchange share: the events that say when its rows have landed."""
+
+    def __init__(self):
+        self.landed = None       # forward: the rows are in this rank's buffer (recorded on the copy stream)
+        self.grad_ready = None   # backward: the gradient rows to send have been produced (compute stream)
+        self.grad_landed = None  # backward: the gradient rows are in this rank's buffer (copy stream)
+
+
+class _DispatchStart(torch.autograd.Function):
+    """Gather the chunk's rows (compute stream), then send them to their destination ranks with copy-engine copies
+    on the copy stream.  Returns this rank's receive buffer, valid once `_AfterLanding` has made the compute stream
+    wait.  Backward: the gradient rows computed here go back the same way and each token's are added up."""
+
+    @staticmethod
+    def forward(ctx, x, plan, transport, flight, keep, slot, tag):
+        if keep:
+            ctx.lease = _Lease(transport, slot)
+        ctx.plan, ctx.transport, ctx.flight, ctx.T, ctx.tag = plan, transport, flight, x.shape[0], tag
+        send = _gather_rows_plain(x, plan.rows)
+        flight.landed, view = transport.send_async(send, plan.send_rows, plan.dispatch_offset, sum(plan.recv_rows),
+                                                   ("dispatch_fwd", slot, tag), plan.token_capacity)
+        return view
+
+    @staticmethod
+    def backward(ctx, g):
+        tr, plan = ctx.transport, ctx.plan
+        landed, back = tr.send_async(g, plan.recv_rows, plan.return_offset, sum(plan.send_rows),
+                                     ("return_bwd", ctx.tag), plan.token_capacity, after=ctx.flight.grad_ready)
+        tr.compute_wait(landed)
+        ctx.lease = None
+        return _sum_rows(back, plan.rows, ctx.T), None, None, None, None, None, None
+
+
+class _AfterLanding(torch.autograd.Function):
+    """Forward: the compute stream waits until the chunk's rows have landed.  Backward: marks, on the compute
+    stream, the moment the gradient of those rows exists -- the copy stream may send it from then on, while the
+    compute stream goes on with other chunks."""
+
+    @staticmethod
+    def forward(ctx, rows, transport, flight):
+        ctx.transport, ctx.flight = transport, flight
+        transport.compute_wait(flight.landed)
+        return rows.view_as(rows)
+
+    @staticmethod
+    def backward(ctx, g):
+        g = g.contiguous()
+        ctx.flight.grad_ready = ctx.transport.mark_compute()
+        return g, None, None
+
+
+class _CombineStart(torch.autograd.Function):
+    """Send the rows computed here for other ranks' tokens back to them (copy stream).  Backward: hands out the
+    output-gradient rows that `_CombineFinish.backward` had the token ranks send here."""
+
+    @staticmethod
+    def forward(ctx, rows, plan, transport, flight, tag):
+        ctx.plan, ctx.transport, ctx.flight, ctx.tag = plan, transport, flight, tag
+        rows = rows.contiguous()
+        flight.landed, view = transport.send_async(rows, plan.recv_rows, plan.return_offset, sum(plan.send_rows),
+                                                   ("return_fwd", tag), plan.token_capacity,
+                                                   after=transport.mark_compute())
+        return view
+
+    @staticmethod
+    def backward(ctx, _unused):
+        ctx.transport.compute_wait(ctx.flight.grad_landed)
+        return ctx.flight.grad_view, None, None, None, None
+
+
+class _CombineFinish(torch.autograd.Function):
+    """Wait for the returned rows and add up each token's.  Backward: gather the output gradient's rows and send
+    them to the expert ranks (asynchronously: the next chunk's backward GEMMs run meanwhile)."""
+
+    @staticmethod
+    def forward(ctx, entries, plan, transport, flight, T, tag):
+        ctx.plan, ctx.transport, ctx.flight, ctx.tag = plan, transport, flight, tag
+        ctx.shape = entries.shape
+        transport.compute_wait(flight.landed)
+        return _sum_rows(entries, plan.rows, T)
+
+    @staticmethod
+    def backward(ctx, g):
+        tr, plan, flight = ctx.transport, ctx.plan, ctx.flight
+        send = _gather_rows_plain(g.contiguous(), plan.rows)
+        flight.grad_landed, flight.grad_view = tr.send_async(send, plan.send_rows, plan.dispatch_offset,
+                                                             sum(plan.recv_rows), ("dispatch_bwd", ctx.tag),
+                                                             plan.token_capacity)
+        # the gradient of `entries` is not a tensor anybody reads: _CombineStart.backward returns the received rows
+        return g.new_zeros(1).expand(ctx.shape), None, None, None, None, None
+
+
+def _gather_rows_plain(x, rows):
+    from . import _lib
+
+    x = x.contiguous()
+    n, H = rows.x_gather_idx.numel(), x.shape[1]
+    dev = x.device
+    with torch.cuda.device(dev):
+        out = torch.empty(n, H, dtype=x.dtype, device=dev)
+        _lib.check(_lib.lib.smoe_gather_sum(x.data_ptr(), out.data_ptr(), None, 0, rows.x_gather_idx.data_ptr(), None,
+                                            n, H, 1, _lib.stream_ptr(dev)), "gather_sum")
+    return out
+
+
+class PipelinedPeerTransport:
+    """Peer-memory transport whose copies run on a second, high-priority stream through the copy engines, so that
+    the exchange of one chunk of tokens overlaps the grouped GEMMs of another (the GEMMs are persistent kernels that
+    occupy every multiprocessor: only copy engines can move data beside them).  The layer cuts its tokens into
+    `micro_batches` chunks; per pass only the first chunk's dispatch and the last chunk's return are exposed."""
+
+    def __init__(self, group, device, micro_batches: int = 2, depth: int = 2):
+        from .peer import AsyncPeerTransport
+
+        self.impl = AsyncPeerTransport(group, device, depth)
+        self.micro_batches = micro_batches
+
+    def dispatch_start(self, x, plan, keep, tag):
+        if tag == 0:
+            self._slot = self.impl.take_slot(keep)
+        flight = _Flight()
+        view = _DispatchStart.apply(x, plan, self.impl, flight, keep and tag == 0, self._slot, tag)
+        return view, flight
+
+    def dispatch_wait(self, handle):
+        view, flight = handle
+        return _AfterLanding.apply(view, self.impl, flight)
+
+    def combine_start(self, rows, plan, tag):
+        flight = _Flight()
+        return _CombineStart.apply(rows, plan, self.impl, flight, tag), flight, tag
+
+    def combine_finish(self, handle, plan, T):
+        entries, flight, tag = handle
+        return _CombineFinish.apply(entries, plan, self.impl, flight, T, tag)
 
     def close(self):
         self.impl.close()
@@ -359,18 +550,19 @@ _default_transports: dict = {}
 
 
 def default_transport(group, x, ops):
-    """Peer memory for bf16 CUDA rows on more than one rank (SONICMOE_EP_TRANSPORT=nccl selects the collective),
-    the collective otherwise.  One peer transport per (process group, device) is kept for functional callers."""
+    """For bf16 CUDA rows on more than one rank: peer memory, pipelined over two chunks of tokens
+    (SONICMOE_EP_TRANSPORT=peer_sync: peer memory, one exchange at a time; =nccl: the collective).  The collective
+    otherwise.  One peer transport per (process group, device) is kept for functional callers."""
     import os
 
     W = dist.get_world_size(group)
-    use_peer = (x.is_cuda and x.dtype == torch.bfloat16 and W > 1
-                and os.environ.get("SONICMOE_EP_TRANSPORT", "peer") == "peer")
-    if not use_peer:
+    kind = os.environ.get("SONICMOE_EP_TRANSPORT", "peer")
+    if not (x.is_cuda and x.dtype == torch.bfloat16 and W > 1 and kind in ("peer", "peer_sync")):
         return CollectiveTransport(group, ops)
-    key = (id(group) if group is not None else None, x.device.index)
+    key = (id(group) if group is not None else None, x.device.index, kind)
     if key not in _default_transports:
-        _default_transports[key] = PeerMemoryTransport(group, x.device)
+        _default_transports[key] = (PipelinedPeerTransport(group, x.device) if kind == "peer" else
+                                    PeerMemoryTransport(group, x.device))
     return _default_transports[key]
 
 
@@ -381,6 +573,9 @@ def close_default_transports() -> None:
     _default_transports.clear()
 
 
+MIN_TOKENS_PER_MICRO_BATCH = 1024
+
+
 def moe_ep_softmax_topk_layer(x, router_w, w1_local, w2_local, K, num_experts, group=None, ops=None,
                               is_inference_mode_enabled=False, logit_bias=None, transport=None):
     """Expert-parallel token-choice top-K layer.
@@ -388,6 +583,12 @@ def moe_ep_softmax_topk_layer(x, router_w, w1_local, w2_local, K, num_experts, g
     x (T_local,H); router_w (E,H) replicated; w1_local (E/W,2I,H), w2_local (E/W,H,I): this rank's experts.
     ``logit_bias`` (E,), optional, is added to the router logits before the top-k (load-skew experiments).
     Returns (o (T_local,H), router_logits (T_local,E), expert_frequency (E,) of this rank's tokens).
+
+    The tokens are cut into ``transport.micro_batches`` chunks (every rank the same number; a rank with few tokens
+    gets short or empty chunks).  Order of work: all chunks' dispatches start; then chunk by chunk the local
+    experts run as soon as that chunk's rows have landed and its results start travelling back; finally every
+    chunk's returned rows are added up.  With a transport that copies asynchronously the exchange of one chunk
+    overlaps the GEMMs of another, in the backward pass as well (autograd runs the mirror image of this order).
     """
     ops = ops or CudaOps()
     W = dist.get_world_size(group)
@@ -403,23 +604,32 @@ def moe_ep_softmax_topk_layer(x, router_w, w1_local, w2_local, K, num_experts, g
     if logit_bias is not None:
         router_logits = router_logits + logit_bias.to(router_logits.dtype)
     scores, indices = ops.topk_softmax(router_logits, K)
+    transport = transport or default_transport(group, x, ops)
+    M = max(1, int(transport.micro_batches))
+    bounds = [T * c // M for c in range(M + 1)]
     with torch.no_grad():
-        plan = plan_dispatch(indices, num_experts, W, group)
+        plans = plan_dispatch(indices, num_experts, W, group, bounds)
         expert_frequency = torch.bincount(indices.reshape(-1).long(), minlength=num_experts).to(torch.int32)
 
-    transport = transport or default_transport(group, x, ops)
-    x_recv = transport.dispatch(x, plan, keep=not inference)
-    s_send = scores.reshape(-1)[plan.pair_slot]
-    s_recv = _AllToAllRows.apply(s_send, plan.send_pairs, plan.recv_pairs, group)
-    with torch.no_grad():
-        meta = _AllToAllRows.apply(torch.stack([plan.pair_row, plan.pair_expert], dim=1), plan.send_pairs,
-                                   plan.recv_pairs, group)
-        tokens = received_pair_tokens(meta[:, 0], plan.recv_rows, plan.recv_pairs)
-        experts = meta[:, 1].contiguous()
-
-    o_recv = ops.local_layer(x_recv, w1_local, w2_local, s_recv, tokens, experts, e_local, inference)
-
-    o = transport.combine(o_recv, plan, T)
+    flights = [transport.dispatch_start(x[bounds[c]:bounds[c + 1]], plans[c], not inference, c) for c in range(M)]
+    routed = []
+    for c, plan in enumerate(plans):
+        s_send = scores[bounds[c]:bounds[c + 1]].reshape(-1)[plan.pair_slot]
+        s_recv = _AllToAllRows.apply(s_send, plan.send_pairs, plan.recv_pairs, group)
+        with torch.no_grad():
+            meta = _AllToAllRows.apply(torch.stack([plan.pair_row, plan.pair_expert], dim=1), plan.send_pairs,
+                                       plan.recv_pairs, group)
+            tokens = received_pair_tokens(meta[:, 0], plan.recv_rows, plan.recv_pairs)
+            experts = meta[:, 1].contiguous()
+        routed.append((s_recv, tokens, experts))
+    returning = []
+    for c, plan in enumerate(plans):
+        x_recv = transport.dispatch_wait(flights[c])
+        s_recv, tokens, experts = routed[c]
+        o_recv = ops.local_layer(x_recv, w1_local, w2_local, s_recv, tokens, experts, e_local, inference)
+        returning.append(transport.combine_start(o_recv, plan, c))
+    outs = [transport.combine_finish(returning[c], plans[c], bounds[c + 1] - bounds[c]) for c in range(M)]
+    o = outs[0] if M == 1 else torch.cat(outs)
     return o, router_logits, expert_frequency
 
 

@@ -169,5 +169,67 @@ class PeerTransport:
         self.leased[slot] = False
 
 
+# Exchange timing (benchmarks): while a list is installed here, send_async appends (start, end) CUDA event pairs
+# recorded on the copy stream around each exchange (copies + barrier).
+exchange_events: list | None = None
+
+
+class AsyncPeerTransport(PeerTransport):
+    """The peer transport with its copies on a second, high-priority stream: `send_async` returns at once with an
+    event; whoever reads the received rows makes its stream wait for that event first.  Segments travel with
+    copy-engine copies only (no kernel), so they run beside kernels that occupy every multiprocessor.  The barrier
+    after each exchange is a one-element all-reduce on a process group of its own, so that it never queues behind
+    the layer's small all-to-alls."""
+
+    def __init__(self, group, device: torch.device, depth: int = 2):
+        super().__init__(group, device, depth)
+        ranks = dist.get_process_group_ranks(group) if group is not None else list(range(dist.get_world_size()))
+        self.barrier_group = dist.new_group(ranks=ranks, backend="nccl")
+        with torch.cuda.device(device):
+            self.comm = torch.cuda.Stream(device=device, priority=-1)
+
+    def mark_compute(self) -> torch.cuda.Event:
+        ev = torch.cuda.Event()
+        ev.record(torch.cuda.current_stream(self.device))
+        return ev
+
+    def compute_wait(self, ev: torch.cuda.Event) -> None:
+        torch.cuda.current_stream(self.device).wait_event(ev)
+
+    def send_async(self, src: torch.Tensor, seg_rows: list[int], dst_offsets: list[int], n_recv: int, key: tuple,
+                   token_capacity: int, after: torch.cuda.Event | None = None):
+        """Segment d of `src` (seg_rows[d] consecutive rows) goes to row dst_offsets[d] of rank d's buffer `key`, once
+        `after` (default: everything issued so far on the current stream) has happened.  Returns (event recorded
+        on the copy stream after the exchange's barrier, this rank's first n_recv rows of the buffer)."""
+        _lib.require_cuda(src, "rows")
+        src = src.contiguous()
+        H = src.shape[1]
+        item = src.element_size()
+        W = self.world
+        buf = self._buffer(key, W * token_capacity * H * item)
+        if after is None:
+            after = self.mark_compute()
+        with torch.cuda.device(self.device), torch.cuda.stream(self.comm):
+            self.comm.wait_event(after)
+            timing = exchange_events is not None
+            if timing:
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(self.comm)
+            ptr = src.data_ptr()
+            stream = self.comm.cuda_stream
+            for d in range(W):
+                nbytes = seg_rows[d] * H * item
+                check(lib.smoe_peer_copy(buf.ptrs[d] + dst_offsets[d] * H * item, ptr, nbytes, stream), "peer_copy")
+                ptr += nbytes
+            dist.all_reduce(self.flag, group=self.barrier_group)
+            if timing:
+                e1.record(self.comm)
+                exchange_events.append((e0, e1))
+            done = torch.cuda.Event()
+            done.record(self.comm)
+        src.record_stream(self.comm)
+        return done, buf.rows(n_recv, H, src.dtype)
+
+
 def lib_max_peers() -> int:
     return 16  # SMOE_MAX_PEERS

@@ -104,13 +104,23 @@ class _EmuCombine(torch.autograd.Function):
 
 
 class EmulatedPeerTransport:
-    """The peer-memory transport's addressing (segment offsets inside the other ranks' buffers) without GPUs."""
+    """The peer-memory transport's addressing (segment offsets inside the other ranks' buffers) without GPUs, with
+    the layer's tokens cut into `micro_batches` chunks as the pipelined transport asks for."""
 
-    def dispatch(self, x, plan, keep):
+    def __init__(self, micro_batches=1):
+        self.micro_batches = micro_batches
+
+    def dispatch_start(self, x, plan, keep, tag):
         return _EmuDispatch.apply(x, plan)
 
-    def combine(self, rows, plan, T):
-        return _EmuCombine.apply(rows, plan, T)
+    def dispatch_wait(self, handle):
+        return handle
+
+    def combine_start(self, rows, plan, tag):
+        return rows
+
+    def combine_finish(self, handle, plan, T):
+        return _EmuCombine.apply(handle, plan, T)
 
 
 def _free_port():
@@ -153,7 +163,7 @@ def _worker(rank, world, port, backend, outdir, use_cuda, use_bias=False, emulat
         if not use_cuda:
             m.ops = OracleOps()
             if emulate_peer:
-                m.transport = EmulatedPeerTransport()
+                m.transport = EmulatedPeerTransport(micro_batches=emulate_peer)
         x = per_rank[rank]["x"].to(dev).requires_grad_(True)
         o, aux = m(x, logit_bias=_logit_bias(E).to(dev) if use_bias else None)
         grads = torch.autograd.grad(o, [x, m.router.weight, m.c_fc.weight, m.c_proj.weight],
@@ -274,10 +284,11 @@ def test_expert_parallel_rank_without_rows_gloo(built_library):
     assert (res[1]["grads"][1] == 0).all() and (res[1]["grads"][2] == 0).all()
 
 
-@pytest.mark.parametrize("world", [2, 4])
-def test_peer_transport_addressing_gloo(built_library, world):
-    """Segments written at the plan's offsets into the other ranks' buffers reproduce the all-to-all's result."""
-    _run_and_check(world, "gloo", use_cuda=False, tol=1e-5, emulate_peer=True)
+@pytest.mark.parametrize("world,micro_batches", [(2, 1), (4, 1), (2, 2), (4, 3)])
+def test_peer_transport_addressing_gloo(built_library, world, micro_batches):
+    """Segments written at the plan's offsets into the other ranks' buffers reproduce the all-to-all's result, also
+    with the tokens cut into chunks that are exchanged and computed one after the other."""
+    _run_and_check(world, "gloo", use_cuda=False, tol=1e-5, emulate_peer=micro_batches)
 
 
 def test_expert_parallel_logit_bias_gloo(built_library):
