@@ -312,11 +312,11 @@ def time_kernels(moe, x, dout, cfg, peaks, reps=5):
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu capture summarised under profiles/
 # (None until a capture exists for the kernel).
-NCU_TRAFFIC_BYTES = {  # profiles/grouped_gemm_pair_T8192_E32_ncu_full.txt, scaled x4 to T=32768, E=128
-    "up_projection_forward": 6.44e9,
-    "down_projection_forward": 3.57e9,
-    "down_projection_backward_act": 5.80e9,
-    "down_projection_weight_grad": 2.63e9,
+NCU_TRAFFIC_BYTES = {  # profiles/grouped_gemm_router_gather_T8192_E32_ncu_full.txt, scaled x4 to T=32768, E=128
+    "up_projection_forward": 6.43e9,
+    "down_projection_forward": 3.56e9,
+    "down_projection_backward_act": 6.17e9,
+    "down_projection_weight_grad": 2.64e9,
     "up_projection_weight_grad": 4.50e9,
     "up_projection_backward_dx": 5.28e9,
 }
