@@ -823,7 +823,7 @@ def run_ep_arm(args, rank, world, local_rank, workload):
                        "collective": ("token rows once per destination rank over peer memory (own gather-and-store "
                                       "kernel + copy-engine copies, NCCL one-element all-reduce as the barrier); "
                                       "scores and indices by NCCL all_to_all_single"
-                                      if world > 1 and os.environ.get("SONICMOE_EP_TRANSPORT", "peer") == "peer" else
+                                      if world > 1 and os.environ.get("SONICMOE_EP_TRANSPORT", "peer").startswith("peer") else
                                       "NCCL all_to_all_single (token rows once per destination rank, scores, indices)"),
                        "routing": "softmax_topk" + (" + per-expert logit bias 2*log(1/rank)" if zipf else ""),
                        "l2_policy": "inputs larger than L2"},

@@ -550,18 +550,19 @@ _default_transports: dict = {}
 
 
 def default_transport(group, x, ops):
-    """For bf16 CUDA rows on more than one rank: peer memory, pipelined over two chunks of tokens
-    (SONICMOE_EP_TRANSPORT=peer_sync: peer memory, one exchange at a time; =nccl: the collective).  The collective
-    otherwise.  One peer transport per (process group, device) is kept for functional callers."""
+    """For bf16 CUDA rows on more than one rank: peer memory, one exchange at a time on the caller's stream
+    (SONICMOE_EP_TRANSPORT=peer_pipelined: peer memory with the tokens cut into two chunks whose exchanges overlap
+    the other chunk's GEMMs; =nccl: the collective).  The collective otherwise.  One peer transport per (process
+    group, device, kind) is kept for functional callers."""
     import os
 
     W = dist.get_world_size(group)
     kind = os.environ.get("SONICMOE_EP_TRANSPORT", "peer")
-    if not (x.is_cuda and x.dtype == torch.bfloat16 and W > 1 and kind in ("peer", "peer_sync")):
+    if not (x.is_cuda and x.dtype == torch.bfloat16 and W > 1 and kind in ("peer", "peer_pipelined")):
         return CollectiveTransport(group, ops)
     key = (id(group) if group is not None else None, x.device.index, kind)
     if key not in _default_transports:
-        _default_transports[key] = (PipelinedPeerTransport(group, x.device) if kind == "peer" else
+        _default_transports[key] = (PipelinedPeerTransport(group, x.device) if kind == "peer_pipelined" else
                                     PeerMemoryTransport(group, x.device))
     return _default_transports[key]
 

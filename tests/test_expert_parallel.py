@@ -354,11 +354,11 @@ def test_expert_parallel_fp8_ops_single_rank_cuda(built_library, fmt):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("transport", ["peer", "peer_sync", "nccl"])
+@pytest.mark.parametrize("transport", ["peer", "peer_pipelined", "nccl"])
 def test_expert_parallel_two_ranks_cuda(built_library, transport, monkeypatch):
-    """Two ranks on two GPUs: rows over peer memory -- pipelined over two chunks of tokens with copy-engine copies on
-    a second stream ("peer", the default), or one exchange at a time with the library's gather-and-store kernel
-    ("peer_sync") -- into buffers mapped through CUDA IPC, and over the NCCL all-to-all."""
+    """Two ranks on two GPUs: rows over peer memory -- one exchange at a time with the library's gather-and-store
+    kernel ("peer", the default), or pipelined over two chunks of tokens with copy-engine copies on a second stream
+    ("peer_pipelined") -- into buffers mapped through CUDA IPC, and over the NCCL all-to-all."""
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     monkeypatch.setenv("SONICMOE_EP_TRANSPORT", transport)
