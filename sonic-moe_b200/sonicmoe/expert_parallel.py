@@ -562,15 +562,24 @@ def default_transport(group, x, ops):
         return CollectiveTransport(group, ops)
     key = (id(group) if group is not None else None, x.device.index, kind)
     if key not in _default_transports:
-        _default_transports[key] = (PipelinedPeerTransport(group, x.device) if kind == "peer_pipelined" else
-                                    PeerMemoryTransport(group, x.device))
+        from .peer import PeerMemoryUnavailable
+
+        try:
+            _default_transports[key] = (PipelinedPeerTransport(group, x.device) if kind == "peer_pipelined" else
+                                        PeerMemoryTransport(group, x.device))
+        except PeerMemoryUnavailable as exc:  # raised on every rank together: all of them take the collective
+            import warnings
+
+            warnings.warn(f"expert-parallel rows go through all_to_all_single: {exc}")
+            _default_transports[key] = CollectiveTransport(group, ops)
     return _default_transports[key]
 
 
 def close_default_transports() -> None:
     """Collective: release the peer-memory buffers of the default transports (before destroying the process group)."""
     for t in _default_transports.values():
-        t.close()
+        if hasattr(t, "close"):
+            t.close()
     _default_transports.clear()
 
 

@@ -38,29 +38,56 @@ class _DeviceMemory:
         self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
 
 
+class PeerMemoryUnavailable(RuntimeError):
+    """Some rank could not allocate, export or map an exchange buffer (raised on every rank of the group)."""
+
+
 class PeerBuffer:
-    """`nbytes` of device memory on this rank, and where every rank's buffer of the same name is mapped here."""
+    """`nbytes` of device memory on this rank, and where every rank's buffer of the same name is mapped here.
+
+    Construction is collective, and so is its failure: every rank reports whether its part worked, and if any
+    rank's did not, all of them undo theirs and raise `PeerMemoryUnavailable` together (no rank is left waiting in a
+    collective for one that gave up)."""
 
     def __init__(self, nbytes: int, group, device: torch.device):
         self.group, self.device, self.nbytes = group, device, nbytes
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.own_ptr, self.ptrs, self.bytes = None, [], None
         with torch.cuda.device(device):
             own = ctypes.c_void_p()
-            check(lib.smoe_peer_alloc(nbytes, ctypes.byref(own)), "peer_alloc")
-            self.own_ptr = own.value
             handle = (ctypes.c_ubyte * 64)()
-            check(lib.smoe_peer_export(self.own_ptr, handle), "peer_export")
+            mine_ok = lib.smoe_peer_alloc(nbytes, ctypes.byref(own)) == 0
+            if mine_ok:
+                self.own_ptr = own.value
+                mine_ok = lib.smoe_peer_export(self.own_ptr, handle) == 0
             handles = [None] * self.world
-            dist.all_gather_object(handles, bytes(handle), group=group)
-            self.ptrs: list[int] = []
-            for r, h in enumerate(handles):
-                if r == self.rank:
-                    self.ptrs.append(self.own_ptr)
-                    continue
-                p = ctypes.c_void_p()
-                raw = (ctypes.c_ubyte * 64).from_buffer_copy(h)
-                check(lib.smoe_peer_open(raw, ctypes.byref(p)), "peer_open")
-                self.ptrs.append(p.value)
+            dist.all_gather_object(handles, bytes(handle) if mine_ok else None, group=group)
+            opened = []
+            if mine_ok and all(h is not None for h in handles):
+                for r, h in enumerate(handles):
+                    if r == self.rank:
+                        self.ptrs.append(self.own_ptr)
+                        continue
+                    p = ctypes.c_void_p()
+                    raw = (ctypes.c_ubyte * 64).from_buffer_copy(h)
+                    if lib.smoe_peer_open(raw, ctypes.byref(p)) != 0:
+                        mine_ok = False
+                        break
+                    opened.append(p.value)
+                    self.ptrs.append(p.value)
+            else:
+                mine_ok = False
+            verdict = torch.tensor([1 if mine_ok else 0], dtype=torch.int32, device=device)
+            dist.all_reduce(verdict, op=dist.ReduceOp.MIN, group=group)
+            if verdict.item() == 0:
+                for p in opened:
+                    lib.smoe_peer_close(p)
+                dist.barrier(group=group)
+                if self.own_ptr is not None:
+                    lib.smoe_peer_free(self.own_ptr)
+                self.own_ptr, self.ptrs = None, []
+                raise PeerMemoryUnavailable("an exchange buffer could not be allocated, exported or mapped on some rank "
+                                            "(CUDA IPC / peer access between the GPUs of this node)")
             self.bytes = torch.as_tensor(_DeviceMemory(self.own_ptr, nbytes), device=device)
 
     def rows(self, n: int, H: int, dtype: torch.dtype) -> torch.Tensor:
@@ -94,6 +121,8 @@ class PeerTransport:
         self.flag = torch.zeros(1, dtype=torch.float32, device=device)
         self.slot = 0
         self.leased = [False] * depth
+        # find out now, together, whether the ranks can map each other's memory at all
+        PeerBuffer(1 << 16, group, device).close()
 
     # -- plumbing ------------------------------------------------------------------------------------------
     def _buffer(self, key: tuple, nbytes: int) -> PeerBuffer:

@@ -465,3 +465,76 @@ def test_dual_tiles_match_single_tiles(smoe, tmp_path):
         results[dual] = torch.load(out)
     for name in ("o", "dx", "dw1", "dw2"):
         assert torch.equal(results["1"][name], results["0"][name]), name
+
+
+@pytest.mark.parametrize("H", [256, 4096])
+def test_gather_sum_to_segments(smoe, H):
+    """The expert-parallel dispatch / return kernel on one GPU: the "other ranks' buffers" are separate local
+    allocations (a peer mapping is just another device pointer to the kernel).  Plain row moves must be bit-exact,
+    weighted per-token sums equal to smoe_gather_sum's."""
+    import ctypes
+
+    _lib, _ = smoe
+    lib = _lib.lib
+    g = torch.Generator().manual_seed(H)
+    T_src, n = 700, 1500
+    src = torch.randn(T_src, H, generator=g).bfloat16().cuda()
+    idx = torch.randint(0, T_src, (n,), generator=g).int().cuda()
+    starts = [0, 400, 400, 1100, n]           # four segments, one of them empty
+    bufs = [torch.full((starts[s + 1] - starts[s] + 3, H), float("nan"), dtype=torch.bfloat16, device="cuda")
+            for s in range(4)]
+    seg_ptr = (ctypes.c_void_p * 4)(*[b.data_ptr() for b in bufs])
+    seg_start = (ctypes.c_int * 5)(*starts)
+    stream = torch.cuda.current_stream().cuda_stream
+    assert lib.smoe_gather_sum_to_peers(src.data_ptr(), None, 0, idx.data_ptr(), None, n, H, 1, seg_ptr, seg_start, 4,
+                                        stream) == 0
+    want = src[idx.long()]
+    for s in range(4):
+        rows = starts[s + 1] - starts[s]
+        assert torch.equal(bufs[s][:rows], want[starts[s]:starts[s + 1]])
+        assert bufs[s][rows:].isnan().all()     # nothing written past a segment's end
+
+    # variable number of source rows per output row, weighted: against smoe_gather_sum on one buffer
+    T_out = 300
+    counts = torch.randint(0, 5, (T_out,), generator=g)
+    off = torch.zeros(T_out + 1, dtype=torch.int32)
+    off[1:] = counts.cumsum(0)
+    m = int(off[-1])
+    rev = torch.randint(0, T_src, (m,), generator=g).int().cuda()
+    w = torch.rand(m, generator=g).cuda()
+    off = off.cuda()
+    ref = torch.empty(T_out, H, dtype=torch.bfloat16, device="cuda")
+    assert lib.smoe_gather_sum(src.data_ptr(), ref.data_ptr(), w.data_ptr(), _lib.SMOE_F32, rev.data_ptr(),
+                               off.data_ptr(), T_out, H, 0, stream) == 0
+    starts = [0, 120, T_out]
+    outs = [torch.empty(starts[s + 1] - starts[s], H, dtype=torch.bfloat16, device="cuda") for s in range(2)]
+    seg_ptr = (ctypes.c_void_p * 2)(*[b.data_ptr() for b in outs])
+    seg_start = (ctypes.c_int * 3)(*starts)
+    assert lib.smoe_gather_sum_to_peers(src.data_ptr(), w.data_ptr(), _lib.SMOE_F32, rev.data_ptr(), off.data_ptr(),
+                                        T_out, H, 0, seg_ptr, seg_start, 2, stream) == 0
+    assert torch.equal(torch.cat(outs), ref)
+    # argument checks: segment table must cover [0, T], pointers 16-byte aligned
+    bad = (ctypes.c_int * 3)(0, 120, T_out - 1)
+    assert lib.smoe_gather_sum_to_peers(src.data_ptr(), None, 0, rev.data_ptr(), off.data_ptr(), T_out, H, 0, seg_ptr,
+                                        bad, 2, stream) == -1
+
+
+def test_peer_buffer_alloc_export_copy(smoe):
+    """Exchange-buffer plumbing that one process can exercise: allocate, export a handle, copy through the copy
+    engine, free.  (Mapping a handle needs a second process: tests/test_expert_parallel.py on two GPUs.)"""
+    import ctypes
+
+    _lib, _ = smoe
+    lib = _lib.lib
+    p = ctypes.c_void_p()
+    assert lib.smoe_peer_alloc(1 << 20, ctypes.byref(p)) == 0 and p.value
+    handle = (ctypes.c_ubyte * 64)()
+    assert lib.smoe_peer_export(p.value, handle) == 0 and any(handle)
+    src = torch.arange(1 << 18, dtype=torch.int32, device="cuda")
+    assert lib.smoe_peer_copy(p.value, src.data_ptr(), 1 << 20, torch.cuda.current_stream().cuda_stream) == 0
+    back = torch.empty_like(src)
+    assert lib.smoe_peer_copy(back.data_ptr(), p.value, 1 << 20, torch.cuda.current_stream().cuda_stream) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(back, src)
+    assert lib.smoe_peer_free(p.value) == 0
+    assert lib.smoe_peer_alloc(0, ctypes.byref(p)) == -1
