@@ -377,10 +377,13 @@ int smoe_peer_copy(void* dst, const void* src, size_t bytes, void* stream);
  * peer stores).  With K = 1 and no weights it is the dispatch of routed token rows fused with their gather;
  * with token_offset it is the return of per-token sums fused with the reduction.  segment_ptr (num_segments)
  * and segment_start (num_segments + 1, first 0, last T) are HOST arrays; num_segments <= SMOE_MAX_PEERS.
+ * The grid walks the output rows from first_row (0 <= first_row < T) round to first_row - 1: ranks that each pass
+ * the first row of their right-hand neighbour's segment write to different destinations at any one time instead of
+ * all to rank 0 first (every link then carries one sender's traffic, not everybody's).
  * The caller orders the ranks (a barrier after the launch) before anybody reads what was written. */
 int smoe_gather_sum_to_peers(const void* src, const void* weights, int weights_dtype, const int* reverse_idx,
                              const int* token_offset, int T, int H, int K, void* const* segment_ptr /* host */,
-                             const int* segment_start /* host */, int num_segments, void* stream);
+                             const int* segment_start /* host */, int num_segments, int first_row, void* stream);
 
 #ifdef __cplusplus
 }

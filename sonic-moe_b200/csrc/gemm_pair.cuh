@@ -56,7 +56,18 @@ struct SharedStorage {
   int m_tile_prefix[MAX_EXPERTS + 1];  // ragged-M: exclusive prefix of ceil(count / 256) per expert
 };
 
-constexpr int SMEM_BYTES = 1024 + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + sizeof(SharedStorage);
+// Output staging of the plain-store epilogues: each epilogue warp owns 32 rows x (payload + 16 B pad).  A thread
+// writes its accumulator row there, the warp reads it back so that consecutive lanes hold consecutive 16-byte pieces
+// of one row, and stores whole 64- or 128-byte row segments: 4 or 8 requests to L2 per store instruction instead of
+// 32 (with one row per lane the epilogue sent about as many requests to L2 as the main loop's operand fetches and
+// competed with them).  Single tiles (4 epilogue warps): 128-byte payload; dual tiles (8 warps): 64-byte payload.
+constexpr int STAGE_OUT_PITCH_WIDE = 144;    // 128 B payload: row r starts 36 words after row r-1 -> conflict-free
+constexpr int STAGE_OUT_PITCH_NARROW = 80;   // 64 B payload
+constexpr int STAGE_OUT_BYTES = 8 * 32 * STAGE_OUT_PITCH_NARROW;  // 20480 >= 4 * 32 * 144
+static_assert(4 * 32 * STAGE_OUT_PITCH_WIDE <= STAGE_OUT_BYTES, "staging area");
+constexpr int SMEM_BYTES =
+    1024 + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + ((sizeof(SharedStorage) + 15) & ~15) + STAGE_OUT_BYTES;
+static_assert(SMEM_BYTES <= 227 * 1024, "shared memory per CTA");
 
 struct Tile {
   int e;
@@ -154,6 +165,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
   uint8_t* sB = smem + NSTAGES * A_STAGE_BYTES;
   uint8_t* sX = sB + NSTAGES * B_STAGE_BYTES;
   SharedStorage& ss = *reinterpret_cast<SharedStorage*>(smem + NSTAGES * (A_STAGE_BYTES + B_STAGE_BYTES + X_STAGE_BYTES));
+  uint8_t* stage_out = reinterpret_cast<uint8_t*>(&ss) + ((sizeof(SharedStorage) + 15) & ~15);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -482,21 +494,32 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
           }
         }
         if (!ok) break;
+        {
+          // stores: 64-byte row segments through this warp's staging rows (8 rows per store instruction)
+          const uint32_t my_stage = smem_u32(stage_out) + (warp - FIRST_EPI_WARP) * (32 * STAGE_OUT_PITCH_NARROW);
 #pragma unroll
-        for (int sub = 0; sub < 2; ++sub) {
-          const int r = tile.row0 + (DUAL == DUAL_M ? sub * 2 * BM : 0) + row_in_tile;
-          const int n0 = tile.n0 + (DUAL == DUAL_N ? sub * BN : 0);
-          if (r < tile.row_end) {
-            __nv_bfloat16* dst = p.out0 + (RAGGED_K ? tile.e * p.out0_expert_stride : 0ll) + r * p.ld0;
+          for (int sub = 0; sub < 2; ++sub) {
+            const int row_base = tile.row0 + (DUAL == DUAL_M ? sub * 2 * BM : 0) + quad * 32;
+            const int n0 = tile.n0 + (DUAL == DUAL_N ? sub * BN : 0);
+            __nv_bfloat16* out = p.out0 + (RAGGED_K ? tile.e * p.out0_expert_stride : 0ll);
 #pragma unroll
             for (int c = 0; c < CHUNKS; ++c) {
               const int n = n0 + (col_half * CHUNKS + c) * 32;
-              if (n < p.N) {
+              if (n >= p.N) break;
 #pragma unroll
-                for (int q = 0; q < 4; ++q)
-                  reinterpret_cast<uint4*>(dst + n)[q] = make_uint4(packed[sub][c * 16 + 4 * q], packed[sub][c * 16 + 4 * q + 1],
-                                                                    packed[sub][c * 16 + 4 * q + 2], packed[sub][c * 16 + 4 * q + 3]);
+              for (int q = 0; q < 4; ++q)
+                st_shared_v4(my_stage + lane * STAGE_OUT_PITCH_NARROW + 16 * q, packed[sub][c * 16 + 4 * q],
+                             packed[sub][c * 16 + 4 * q + 1], packed[sub][c * 16 + 4 * q + 2],
+                             packed[sub][c * 16 + 4 * q + 3]);
+              __syncwarp();
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const int rr = 8 * i + (lane >> 2);
+                const uint4 w = ld_shared_v4(my_stage + rr * STAGE_OUT_PITCH_NARROW + 16 * (lane & 3));
+                const int r = row_base + rr;
+                if (r < tile.row_end) *reinterpret_cast<uint4*>(out + r * p.ld0 + n + 8 * (lane & 3)) = w;
               }
+              __syncwarp();
             }
           }
         }
@@ -554,6 +577,48 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
               const int n = n0 + (col_half * CHUNKS + c) * 32;
               if (n < p.N) epilogue_chunk<EPI, RAGGED_K>(p, tile.e, r, n, v[c], score, ds_acc);
             }
+          }
+        } else if constexpr (EPI == EPI_STORE && EW == 4) {
+          // plain stores of single tiles: two 32-column chunks (a 128-byte row segment) at a time through this warp's
+          // staging rows, 4 full rows per store instruction
+          const uint32_t my_stage = smem_u32(stage_out) + (warp - FIRST_EPI_WARP) * (32 * STAGE_OUT_PITCH_WIDE);
+          const int row_base = tile.row0 + quad * 32;
+          __nv_bfloat16* out = p.out0 + (RAGGED_K ? tile.e * p.out0_expert_stride : 0ll);
+#pragma unroll 1
+          for (int c = 0; c < COLS_PER_WARP / 32; c += 2) {
+            const int n = n0 + c * 32;
+            if (n >= p.N) break;  // N is a multiple of 64: both chunks exist or neither
+            uint32_t v0[32], v1[32];
+            if (have_acc) {
+              tmem_ld32(t_addr + c * 32, v0);
+              tmem_ld32(t_addr + (c + 1) * 32, v1);
+              tmem_ld_wait();
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v0[j] = v1[j] = 0u;
+            }
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              st_shared_v4(my_stage + lane * STAGE_OUT_PITCH_WIDE + 16 * q,
+                           pack_bf16(__uint_as_float(v0[8 * q]), __uint_as_float(v0[8 * q + 1])),
+                           pack_bf16(__uint_as_float(v0[8 * q + 2]), __uint_as_float(v0[8 * q + 3])),
+                           pack_bf16(__uint_as_float(v0[8 * q + 4]), __uint_as_float(v0[8 * q + 5])),
+                           pack_bf16(__uint_as_float(v0[8 * q + 6]), __uint_as_float(v0[8 * q + 7])));
+              st_shared_v4(my_stage + lane * STAGE_OUT_PITCH_WIDE + 64 + 16 * q,
+                           pack_bf16(__uint_as_float(v1[8 * q]), __uint_as_float(v1[8 * q + 1])),
+                           pack_bf16(__uint_as_float(v1[8 * q + 2]), __uint_as_float(v1[8 * q + 3])),
+                           pack_bf16(__uint_as_float(v1[8 * q + 4]), __uint_as_float(v1[8 * q + 5])),
+                           pack_bf16(__uint_as_float(v1[8 * q + 6]), __uint_as_float(v1[8 * q + 7])));
+            }
+            __syncwarp();
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int rr = 4 * i + (lane >> 3);
+              const uint4 w = ld_shared_v4(my_stage + rr * STAGE_OUT_PITCH_WIDE + 16 * (lane & 7));
+              const int rw = row_base + rr;
+              if (rw < tile.row_end) *reinterpret_cast<uint4*>(out + rw * p.ld0 + n + 8 * (lane & 7)) = w;
+            }
+            __syncwarp();
           }
         } else {
 #pragma unroll 1

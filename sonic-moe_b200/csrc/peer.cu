@@ -28,11 +28,14 @@ __global__ void __launch_bounds__(256) gather_sum_to_segments_kernel(const __nv_
                                                                      const W* __restrict__ w,
                                                                      const int* __restrict__ rev,
                                                                      const int* __restrict__ tok_off, int T, int H,
-                                                                     int K, const PeerSegments seg) {
+                                                                     int K, int first_row, const PeerSegments seg) {
   const int vec_per_row = H >> 3;
   const long long g = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (g >= static_cast<long long>(T) * vec_per_row) return;
-  const int t = static_cast<int>(g / vec_per_row);
+  // the grid walks the output rows starting at first_row and wrapping around: ranks that all start with the segment
+  // of their right-hand neighbour never write to the same destination at the same time
+  int t = static_cast<int>(g / vec_per_row) + first_row;
+  if (t >= T) t -= T;
   const int c = static_cast<int>(g % vec_per_row);
   int s = 0;
   while (s + 1 < seg.n && t >= seg.start[s + 1]) ++s;
@@ -117,8 +120,9 @@ int smoe_peer_copy(void* dst, const void* src, size_t bytes, void* stream) {
 
 int smoe_gather_sum_to_peers(const void* src, const void* weights, int weights_dtype, const int* reverse_idx,
                              const int* token_offset, int T, int H, int K, void* const* segment_ptr,
-                             const int* segment_start, int num_segments, void* stream) {
+                             const int* segment_start, int num_segments, int first_row, void* stream) {
   if (T < 0 || H <= 0 || (H % 8) != 0 || num_segments <= 0 || num_segments > SMOE_MAX_PEERS) return SMOE_ERR_SHAPE;
+  if (first_row < 0 || (T > 0 && first_row >= T)) return SMOE_ERR_SHAPE;
   if (token_offset == nullptr && K <= 0) return SMOE_ERR_SHAPE;
   if (segment_ptr == nullptr || segment_start == nullptr) return SMOE_ERR_SHAPE;
   if (segment_start[0] != 0 || segment_start[num_segments] != T) return SMOE_ERR_SHAPE;
@@ -140,10 +144,10 @@ int smoe_gather_sum_to_peers(const void* src, const void* weights, int weights_d
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (weights == nullptr || weights_dtype == SMOE_F32)
     gather_sum_to_segments_kernel<float><<<grid, 256, 0, st>>>(s_, static_cast<const float*>(weights), reverse_idx,
-                                                                token_offset, T, H, K, seg);
+                                                                token_offset, T, H, K, first_row, seg);
   else if (weights_dtype == SMOE_BF16)
     gather_sum_to_segments_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(
-        s_, static_cast<const __nv_bfloat16*>(weights), reverse_idx, token_offset, T, H, K, seg);
+        s_, static_cast<const __nv_bfloat16*>(weights), reverse_idx, token_offset, T, H, K, first_row, seg);
   else
     return SMOE_ERR_DTYPE;
   return cudaGetLastError() == cudaSuccess ? SMOE_OK : SMOE_ERR_LAUNCH;

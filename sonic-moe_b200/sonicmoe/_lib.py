@@ -89,7 +89,7 @@ SIGNATURES: dict[str, tuple] = {
     "smoe_peer_open": (I, [P, P]),
     "smoe_peer_close": (I, [P]),
     "smoe_peer_copy": (I, [P, P, c_size_t, P]),
-    "smoe_gather_sum_to_peers": (I, [P, P, I, P, P, I, I, I, P, P, I, P]),
+    "smoe_gather_sum_to_peers": (I, [P, P, I, P, P, I, I, I, P, P, I, I, P]),
 }
 
 

@@ -77,9 +77,9 @@ class PeerBuffer:
                     self.ptrs.append(p.value)
             else:
                 mine_ok = False
-            verdict = torch.tensor([1 if mine_ok else 0], dtype=torch.int32, device=device)
-            dist.all_reduce(verdict, op=dist.ReduceOp.MIN, group=group)
-            if verdict.item() == 0:
+            all_ok = torch.tensor([1 if mine_ok else 0], dtype=torch.int32, device=device)
+            dist.all_reduce(all_ok, op=dist.ReduceOp.MIN, group=group)
+            if all_ok.item() == 0:
                 for p in opened:
                     lib.smoe_peer_close(p)
                 dist.barrier(group=group)
@@ -159,9 +159,15 @@ class PeerTransport:
         for d in range(W):
             starts.append(starts[-1] + plan.send_rows[d])
         seg_start = (ctypes.c_int * (W + 1))(*starts)
+        # start with the right-hand neighbour's segment (wrapping round to this rank's own last): at any moment the
+        # ranks then write to different destinations
+        first = starts[(self.rank + 1) % W] if n > 0 else 0
+        if first >= n:
+            first = 0
         with torch.cuda.device(self.device):
             check(lib.smoe_gather_sum_to_peers(x.data_ptr(), None, 0, plan.rows.x_gather_idx.data_ptr(), None, n, H, 1,
-                                               seg_ptr, seg_start, W, stream_ptr(self.device)), "gather_sum_to_peers")
+                                               seg_ptr, seg_start, W, first, stream_ptr(self.device)),
+                  "gather_sum_to_peers")
             self._barrier()
         return buf.rows(sum(plan.recv_rows), H, x.dtype)
 
@@ -176,11 +182,14 @@ class PeerTransport:
         buf = self._buffer(key, W * plan.token_capacity * H * item)
         with torch.cuda.device(self.device):
             stream = stream_ptr(self.device)
-            src = rows.data_ptr()
+            starts = [0]
             for s in range(W):
-                nbytes = plan.recv_rows[s] * H * item
-                check(lib.smoe_peer_copy(buf.ptrs[s] + plan.return_offset[s] * H * item, src, nbytes, stream), "peer_copy")
-                src += nbytes
+                starts.append(starts[-1] + plan.recv_rows[s])
+            for k in range(1, W + 1):  # right-hand neighbour first, this rank's own segment last (see dispatch_rows)
+                s = (self.rank + k) % W
+                check(lib.smoe_peer_copy(buf.ptrs[s] + plan.return_offset[s] * H * item,
+                                         rows.data_ptr() + starts[s] * H * item, plan.recv_rows[s] * H * item, stream),
+                      "peer_copy")
             self._barrier()
         return buf.rows(sum(plan.send_rows), H, rows.dtype)
 
@@ -244,12 +253,14 @@ class AsyncPeerTransport(PeerTransport):
             if timing:
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 e0.record(self.comm)
-            ptr = src.data_ptr()
             stream = self.comm.cuda_stream
+            starts = [0]
             for d in range(W):
-                nbytes = seg_rows[d] * H * item
-                check(lib.smoe_peer_copy(buf.ptrs[d] + dst_offsets[d] * H * item, ptr, nbytes, stream), "peer_copy")
-                ptr += nbytes
+                starts.append(starts[-1] + seg_rows[d])
+            for k in range(1, W + 1):  # right-hand neighbour first: no two ranks copy to the same destination at once
+                d = (self.rank + k) % W
+                check(lib.smoe_peer_copy(buf.ptrs[d] + dst_offsets[d] * H * item, src.data_ptr() + starts[d] * H * item,
+                                         seg_rows[d] * H * item, stream), "peer_copy")
             dist.all_reduce(self.flag, group=self.barrier_group)
             if timing:
                 e1.record(self.comm)

@@ -45,8 +45,8 @@ def test_queries_and_argument_checks_without_gpu(built_library):
     assert lib.smoe_topk_softmax(None, 7, None, None, 4, 8, 2, None) == -6      # unknown dtype
     assert lib.smoe_gather_sum(None, None, None, 0, None, None, 4, 12, 2, None) == -1  # H % 8
     # expert-parallel kernel: segment table checked on the host before anything is launched
-    assert lib.smoe_gather_sum_to_peers(None, None, 0, None, None, 8, 64, 1, None, None, 0, None) == -1
-    assert lib.smoe_gather_sum_to_peers(None, None, 0, None, None, 8, 64, 1, None, None, 17, None) == -1
+    assert lib.smoe_gather_sum_to_peers(None, None, 0, None, None, 8, 64, 1, None, None, 0, 0, None) == -1
+    assert lib.smoe_gather_sum_to_peers(None, None, 0, None, None, 8, 64, 1, None, None, 17, 0, None) == -1
     assert lib.smoe_router_forward_supported(4096, 128, 8) == 1
     assert lib.smoe_router_forward_supported(4096, 8, 2) == 0 and lib.smoe_router_forward_supported(4096, 128, 17) == 0
     # empty problems are no-ops

@@ -486,7 +486,7 @@ def test_gather_sum_to_segments(smoe, H):
     seg_ptr = (ctypes.c_void_p * 4)(*[b.data_ptr() for b in bufs])
     seg_start = (ctypes.c_int * 5)(*starts)
     stream = torch.cuda.current_stream().cuda_stream
-    assert lib.smoe_gather_sum_to_peers(src.data_ptr(), None, 0, idx.data_ptr(), None, n, H, 1, seg_ptr, seg_start, 4,
+    assert lib.smoe_gather_sum_to_peers(src.data_ptr(), None, 0, idx.data_ptr(), None, n, H, 1, seg_ptr, seg_start, 4, 777,
                                         stream) == 0
     want = src[idx.long()]
     for s in range(4):
@@ -511,12 +511,12 @@ def test_gather_sum_to_segments(smoe, H):
     seg_ptr = (ctypes.c_void_p * 2)(*[b.data_ptr() for b in outs])
     seg_start = (ctypes.c_int * 3)(*starts)
     assert lib.smoe_gather_sum_to_peers(src.data_ptr(), w.data_ptr(), _lib.SMOE_F32, rev.data_ptr(), off.data_ptr(),
-                                        T_out, H, 0, seg_ptr, seg_start, 2, stream) == 0
+                                        T_out, H, 0, seg_ptr, seg_start, 2, 0, stream) == 0
     assert torch.equal(torch.cat(outs), ref)
     # argument checks: segment table must cover [0, T], pointers 16-byte aligned
     bad = (ctypes.c_int * 3)(0, 120, T_out - 1)
     assert lib.smoe_gather_sum_to_peers(src.data_ptr(), None, 0, rev.data_ptr(), off.data_ptr(), T_out, H, 0, seg_ptr,
-                                        bad, 2, stream) == -1
+                                        bad, 2, 0, stream) == -1
 
 
 def test_peer_buffer_alloc_export_copy(smoe):
