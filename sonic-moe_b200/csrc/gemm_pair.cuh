@@ -149,6 +149,65 @@ __device__ __forceinline__ int unit_num_kb(const GemmParams& p, long long t, lon
   }
 }
 
+// Warp-cooperative row I/O through a warp's staging rows (32 rows of PITCH bytes).  Lane l owns row l of a 32-row
+// block; global memory is touched with consecutive lanes on consecutive 16-byte pieces of one row, so an instruction
+// moves whole 64- or 128-byte row segments.  Rows at or beyond row_end are skipped.  Every lane must call.
+template <int PITCH>
+__device__ __forceinline__ void warp_store_rows64(uint32_t stage, int lane, const uint32_t (&w)[16], __nv_bfloat16* out,
+                                                  long long ld, int row_base, int row_end, int col) {
+#pragma unroll
+  for (int q = 0; q < 4; ++q) st_shared_v4(stage + lane * PITCH + 16 * q, w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
+  __syncwarp();
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int rr = 8 * i + (lane >> 2);
+    const uint4 v = ld_shared_v4(stage + rr * PITCH + 16 * (lane & 3));
+    if (row_base + rr < row_end) *reinterpret_cast<uint4*>(out + (row_base + rr) * ld + col + 8 * (lane & 3)) = v;
+  }
+  __syncwarp();
+}
+
+template <int PITCH>
+__device__ __forceinline__ void warp_store_rows128(uint32_t stage, int lane, const uint32_t (&w)[32], __nv_bfloat16* out,
+                                                   long long ld, int row_base, int row_end, int col) {
+  static_assert(PITCH >= 128 + 16, "128-byte payload");
+#pragma unroll
+  for (int q = 0; q < 8; ++q) st_shared_v4(stage + lane * PITCH + 16 * q, w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
+  __syncwarp();
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int rr = 4 * i + (lane >> 3);
+    const uint4 v = ld_shared_v4(stage + rr * PITCH + 16 * (lane & 7));
+    if (row_base + rr < row_end) *reinterpret_cast<uint4*>(out + (row_base + rr) * ld + col + 8 * (lane & 7)) = v;
+  }
+  __syncwarp();
+}
+
+// The inverse: 32 rows x 128 bytes read with whole-row-segment loads; lane l ends with row l (zeros past row_end).
+template <int PITCH>
+__device__ __forceinline__ void warp_load_rows128(uint32_t stage, int lane, uint32_t (&w)[32], const __nv_bfloat16* src,
+                                                  long long ld, int row_base, int row_end, int col) {
+  static_assert(PITCH >= 128 + 16, "128-byte payload");
+  uint4 v[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int rr = 4 * i + (lane >> 3);
+    v[i] = make_uint4(0u, 0u, 0u, 0u);
+    if (row_base + rr < row_end)
+      v[i] = *reinterpret_cast<const uint4*>(src + (row_base + rr) * ld + col + 8 * (lane & 7));
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+    st_shared_v4(stage + (4 * i + (lane >> 3)) * PITCH + 16 * (lane & 7), v[i].x, v[i].y, v[i].z, v[i].w);
+  __syncwarp();
+#pragma unroll
+  for (int q = 0; q < 8; ++q) {
+    const uint4 t = ld_shared_v4(stage + lane * PITCH + 16 * q);
+    w[4 * q] = t.x; w[4 * q + 1] = t.y; w[4 * q + 2] = t.z; w[4 * q + 3] = t.w;
+  }
+  __syncwarp();
+}
+
 template <bool RAGGED_K, bool A_GATHER, bool A_MN, bool B_GATHER, bool B_MN, int EPI, int EW, int GW,
           int DUAL = DUAL_NONE>
 __global__ void __launch_bounds__(threads(EW, GW, DUAL != 0), 1)
@@ -571,12 +630,79 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
 #pragma unroll
               for (int j = 0; j < 32; ++j) v[c][j] = 0u;
           }
-          if (row_ok) {
+          if constexpr (EPI == EPI_SWIGLU) {
+            // z (unless not wanted) and y1 = silu(gate) * up leave through the warp's staging rows as 64-byte row
+            // segments: one per 32 accumulator columns for z, one per 64 for y1 (N = 2I is a multiple of 128, so
+            // chunks come in pairs)
+            const uint32_t my_stage = smem_u32(stage_out) + (warp - FIRST_EPI_WARP) * (32 * STAGE_OUT_PITCH_NARROW);
+            const int row_base = r - lane;
+            uint32_t yp[16];
+#pragma unroll
+            for (int c = 0; c < CHUNKS; ++c) {
+              const int n = n0 + (col_half * CHUNKS + c) * 32;
+              if (n >= p.N) break;
+              uint32_t zp[16];
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                const float g = __uint_as_float(v[c][2 * j]);
+                const float u = __uint_as_float(v[c][2 * j + 1]);
+                zp[j] = pack_bf16(g, u);
+                v[c][j] = __float_as_uint(g * sigmoid_f(g) * u);  // the chunk's 16 products, kept in place
+              }
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                yp[(c & 1) * 8 + j] = pack_bf16(__uint_as_float(v[c][2 * j]), __uint_as_float(v[c][2 * j + 1]));
+              if (p.out0 != nullptr)
+                warp_store_rows64<STAGE_OUT_PITCH_NARROW>(my_stage, lane, zp, p.out0, p.ld0, row_base, tile.row_end, n);
+              if (c & 1)
+                warp_store_rows64<STAGE_OUT_PITCH_NARROW>(my_stage, lane, yp, p.out1, p.ld1, row_base, tile.row_end,
+                                                          (n - 32) >> 1);
+            }
+          } else if (row_ok) {
 #pragma unroll
             for (int c = 0; c < CHUNKS; ++c) {
               const int n = n0 + (col_half * CHUNKS + c) * 32;
               if (n < p.N) epilogue_chunk<EPI, RAGGED_K>(p, tile.e, r, n, v[c], score, ds_acc);
             }
+          }
+        } else if constexpr (EPI == EPI_DSWIGLU && EW == 4) {
+          // dSwiGLU of single tiles, 32 accumulator columns at a time: the 128-byte piece of the saved pre-activation
+          // row comes in, and the dz (128 B) and y1*s (64 B) pieces go out, through this warp's staging rows with
+          // whole-row-segment accesses; the arithmetic stays one row per thread.
+          const uint32_t my_stage = smem_u32(stage_out) + (warp - FIRST_EPI_WARP) * (32 * STAGE_OUT_PITCH_WIDE);
+          const int row_base = tile.row0 + quad * 32;
+#pragma unroll 1
+          for (int c = 0; c < COLS_PER_WARP / 32; ++c) {
+            const int n = n0 + c * 32;
+            if (n >= p.N) break;
+            uint32_t v[32], zw[32];
+            if (have_acc) tmem_ld32(t_addr + c * 32, v);
+            warp_load_rows128<STAGE_OUT_PITCH_WIDE>(my_stage, lane, zw, p.z, 2ll * p.N, row_base, tile.row_end, 2 * n);
+            if (have_acc) {
+              tmem_ld_wait();
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] = 0u;
+            }
+            uint32_t ys[16];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const __nv_bfloat162 gu = *reinterpret_cast<const __nv_bfloat162*>(&zw[i]);
+              const float g = __low2float(gu), u = __high2float(gu);
+              const float dy = __uint_as_float(v[i]);
+              const float sig = sigmoid_f(g);
+              const float silu = g * sig;
+              const float y1 = silu * u;
+              ds_acc += dy * y1;
+              const float dg = dy * u * (sig * (1.f + g * (1.f - sig))) * score;
+              const float du = dy * silu * score;
+              zw[i] = pack_bf16(dg, du);
+              v[i] = __float_as_uint(y1 * score);
+            }
+#pragma unroll
+            for (int j = 0; j < 16; ++j) ys[j] = pack_bf16(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]));
+            warp_store_rows128<STAGE_OUT_PITCH_WIDE>(my_stage, lane, zw, p.out0, p.ld0, row_base, tile.row_end, 2 * n);
+            warp_store_rows64<STAGE_OUT_PITCH_WIDE>(my_stage, lane, ys, p.out1, p.ld1, row_base, tile.row_end, n);
           }
         } else if constexpr (EPI == EPI_STORE && EW == 4) {
           // plain stores of single tiles: two 32-column chunks (a 128-byte row segment) at a time through this warp's
