@@ -116,9 +116,10 @@ static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmPara
     // than an eighth of the MMA work (e.g. N = 768)
     const int doubled = A_GATHER ? p.N : p.M;
     const bool fits = ((doubled + 511) / 512 * 512 - doubled) * 8 <= doubled;
-    // Not for the activation-gradient epilogues: with both accumulators belonging to one unit, the next unit's
-    // second MMA group waits until the first accumulator's dSwiGLU arithmetic, z loads and stores are through
-    // (measured at the benchmark shape: 2.72-2.75 ms dual against 2.38-2.44 ms single, same process).
+    // The activation-gradient epilogues keep single tiles: with both accumulators belonging to one unit the next
+    // unit's second MMA group waits for the first accumulator's dSwiGLU pass.  Measured at the benchmark shape with
+    // that pass staged through shared memory like the single-tile one: step 17.75-17.97 ms dual against 17.88-18.13 ms
+    // single in alternating runs, the kernel alone 2.26-2.69 against 2.09-2.58 ms -- no gain worth a second variant.
     if constexpr (EPI != EPI_DSWIGLU && EPI != EPI_DACT) {
     if (use_dual_tiles() && fits) {
       constexpr int kDual = A_GATHER ? pair::DUAL_N : pair::DUAL_M;
