@@ -313,12 +313,12 @@ def time_kernels(moe, x, dout, cfg, peaks, reps=5):
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu capture summarised under profiles/
 # (None until a capture exists for the kernel).
 NCU_TRAFFIC_BYTES = {  # profiles/grouped_gemm_router_gather_T8192_E32_ncu_full.txt, scaled x4 to T=32768, E=128
-    "up_projection_forward": 6.43e9,
-    "down_projection_forward": 3.56e9,
-    "down_projection_backward_act": 6.17e9,
-    "down_projection_weight_grad": 2.64e9,
-    "up_projection_weight_grad": 4.50e9,
-    "up_projection_backward_dx": 5.28e9,
+    "up_projection_forward": 6.53e9,
+    "down_projection_forward": 3.59e9,
+    "down_projection_backward_act": 6.29e9,
+    "down_projection_weight_grad": 2.74e9,
+    "up_projection_weight_grad": 4.60e9,
+    "up_projection_backward_dx": 5.37e9,
 }
 
 
