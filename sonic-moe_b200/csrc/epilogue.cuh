@@ -129,6 +129,65 @@ __device__ __forceinline__ void store_bf16x32(__nv_bfloat16* dst, const float (&
   }
 }
 
+// Warp-cooperative row I/O through a warp's staging rows (32 rows of PITCH bytes).  Lane l owns row l of a 32-row
+// block; global memory is touched with consecutive lanes on consecutive 16-byte pieces of one row, so an instruction
+// moves whole 64- or 128-byte row segments.  Rows at or beyond row_end are skipped.  Every lane must call.
+template <int PITCH>
+__device__ __forceinline__ void warp_store_rows64(uint32_t stage, int lane, const uint32_t (&w)[16], __nv_bfloat16* out,
+                                                  long long ld, int row_base, int row_end, int col) {
+#pragma unroll
+  for (int q = 0; q < 4; ++q) st_shared_v4(stage + lane * PITCH + 16 * q, w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
+  __syncwarp();
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int rr = 8 * i + (lane >> 2);
+    const uint4 v = ld_shared_v4(stage + rr * PITCH + 16 * (lane & 3));
+    if (row_base + rr < row_end) *reinterpret_cast<uint4*>(out + (row_base + rr) * ld + col + 8 * (lane & 3)) = v;
+  }
+  __syncwarp();
+}
+
+template <int PITCH>
+__device__ __forceinline__ void warp_store_rows128(uint32_t stage, int lane, const uint32_t (&w)[32], __nv_bfloat16* out,
+                                                   long long ld, int row_base, int row_end, int col) {
+  static_assert(PITCH >= 128 + 16, "128-byte payload");
+#pragma unroll
+  for (int q = 0; q < 8; ++q) st_shared_v4(stage + lane * PITCH + 16 * q, w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
+  __syncwarp();
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int rr = 4 * i + (lane >> 3);
+    const uint4 v = ld_shared_v4(stage + rr * PITCH + 16 * (lane & 7));
+    if (row_base + rr < row_end) *reinterpret_cast<uint4*>(out + (row_base + rr) * ld + col + 8 * (lane & 7)) = v;
+  }
+  __syncwarp();
+}
+
+// The inverse: 32 rows x 128 bytes read with whole-row-segment loads; lane l ends with row l (zeros past row_end).
+template <int PITCH>
+__device__ __forceinline__ void warp_load_rows128(uint32_t stage, int lane, uint32_t (&w)[32], const __nv_bfloat16* src,
+                                                  long long ld, int row_base, int row_end, int col) {
+  static_assert(PITCH >= 128 + 16, "128-byte payload");
+  uint4 v[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int rr = 4 * i + (lane >> 3);
+    v[i] = make_uint4(0u, 0u, 0u, 0u);
+    if (row_base + rr < row_end)
+      v[i] = *reinterpret_cast<const uint4*>(src + (row_base + rr) * ld + col + 8 * (lane & 7));
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+    st_shared_v4(stage + (4 * i + (lane >> 3)) * PITCH + 16 * (lane & 7), v[i].x, v[i].y, v[i].z, v[i].w);
+  __syncwarp();
+#pragma unroll
+  for (int q = 0; q < 8; ++q) {
+    const uint4 t = ld_shared_v4(stage + lane * PITCH + 16 * q);
+    w[4 * q] = t.x; w[4 * q + 1] = t.y; w[4 * q + 2] = t.z; w[4 * q + 3] = t.w;
+  }
+  __syncwarp();
+}
+
 // acc (+ bias) as 32 floats
 __device__ __forceinline__ void load_biased(const GemmParams& p, int expert, int n, const uint32_t (&v)[32],
                                             float (&f)[32]) {
@@ -191,6 +250,70 @@ __device__ __forceinline__ void dswiglu_chunk(const GemmParams& p, int r, int n,
         v[8 * j + i] = dzw[i];
         amax = fmaxf(amax, fmaxf(fabsf(__uint_as_float(dzw[i] << 16)), fabsf(__uint_as_float(dzw[i] & 0xFFFF0000u))));
       }
+    }
+  }
+}
+
+// 64-byte variant of warp_load_rows128 (staging rows of PITCH >= 80 bytes).
+template <int PITCH>
+__device__ __forceinline__ void warp_load_rows64(uint32_t stage, int lane, uint32_t (&w)[16], const __nv_bfloat16* src,
+                                                 long long ld, int row_base, int row_end, int col) {
+  uint4 v[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int rr = 8 * i + (lane >> 2);
+    v[i] = make_uint4(0u, 0u, 0u, 0u);
+    if (row_base + rr < row_end)
+      v[i] = *reinterpret_cast<const uint4*>(src + (row_base + rr) * ld + col + 8 * (lane & 3));
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+    st_shared_v4(stage + (8 * i + (lane >> 2)) * PITCH + 16 * (lane & 3), v[i].x, v[i].y, v[i].z, v[i].w);
+  __syncwarp();
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    const uint4 t = ld_shared_v4(stage + lane * PITCH + 16 * q);
+    w[4 * q] = t.x; w[4 * q + 1] = t.y; w[4 * q + 2] = t.z; w[4 * q + 3] = t.w;
+  }
+  __syncwarp();
+}
+
+// dswiglu_chunk with the row traffic (z in, dz and y1 * score out) going through the warp's staging rows as 64-byte
+// row segments.  Every lane of the warp must call (lane l owns row row_base + l; rows at or past row_end read zeros
+// and store nothing).  Same arithmetic, same results.
+template <bool KEEP, int PITCH>
+__device__ __forceinline__ void dswiglu_chunk_staged(const GemmParams& p, uint32_t stage, int lane, int row_base,
+                                                     int row_end, int n, uint32_t (&v)[32], float score, float& ds_acc,
+                                                     float& amax) {
+  uint32_t za[16], zb[16], ys[16];
+  warp_load_rows64<PITCH>(stage, lane, za, p.z, 2ll * p.N, row_base, row_end, 2 * n);
+  warp_load_rows64<PITCH>(stage, lane, zb, p.z, 2ll * p.N, row_base, row_end, 2 * n + 32);
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    uint32_t& zw = i < 16 ? za[i] : zb[i - 16];
+    const __nv_bfloat162 gu = *reinterpret_cast<const __nv_bfloat162*>(&zw);
+    const float g = __low2float(gu), u = __high2float(gu);
+    const float dy = __uint_as_float(v[i]);
+    const float sig = sigmoid_f(g);
+    const float silu = g * sig;
+    const float y1 = silu * u;
+    ds_acc += dy * y1;
+    const float dg = dy * u * (sig * (1.f + g * (1.f - sig))) * score;
+    const float du = dy * silu * score;
+    zw = pack_bf16(dg, du);
+    v[i] = __float_as_uint(y1 * score);
+  }
+#pragma unroll
+  for (int j = 0; j < 16; ++j) ys[j] = pack_bf16(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]));
+  warp_store_rows64<PITCH>(stage, lane, za, p.out0, p.ld0, row_base, row_end, 2 * n);
+  warp_store_rows64<PITCH>(stage, lane, zb, p.out0, p.ld0, row_base, row_end, 2 * n + 32);
+  warp_store_rows64<PITCH>(stage, lane, ys, p.out1, p.ld1, row_base, row_end, n);
+  if constexpr (KEEP) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      const uint32_t w = i < 16 ? za[i] : zb[i - 16];
+      v[i] = w;
+      amax = fmaxf(amax, fmaxf(fabsf(__uint_as_float(w << 16)), fabsf(__uint_as_float(w & 0xFFFF0000u))));
     }
   }
 }

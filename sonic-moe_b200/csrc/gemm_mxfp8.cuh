@@ -72,8 +72,13 @@ struct SharedStorage {
   int m_tile_prefix[MAX_EXPERTS + 1];
 };
 
-constexpr int SMEM_BYTES =
-    1024 + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + SF_SETS * SF_SET_BYTES + sizeof(SharedStorage);
+// Output staging: 32 rows x 80 bytes per epilogue warp, so that bf16 outputs leave as 64-byte row segments (8 rows
+// per store instruction) instead of one row per lane (see warp_store_rows64 in epilogue.cuh).
+constexpr int STAGE_OUT_PITCH = 80;
+constexpr int STAGE_OUT_BYTES = EPI_WARPS * 32 * STAGE_OUT_PITCH;  // 20 KiB
+constexpr int SMEM_BYTES = 1024 + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + SF_SETS * SF_SET_BYTES +
+                           ((sizeof(SharedStorage) + 15) & ~15) + STAGE_OUT_BYTES;
+static_assert(SMEM_BYTES <= 227 * 1024, "shared memory per CTA");
 
 // Instruction descriptor of the block-scaled kinds: no accumulator-format field (always fp32); scale-factor
 // byte selectors for B (bits 4-5) and A (bits 29-30); bit 23 = scale factors are UE8M0.
@@ -121,6 +126,7 @@ grouped_gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
   uint8_t* sB = smem + STAGES * A_STAGE_BYTES;
   uint8_t* sSF = smem + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES);
   SharedStorage& ss = *reinterpret_cast<SharedStorage*>(sSF + SF_SETS * SF_SET_BYTES);
+  uint8_t* stage_out = reinterpret_cast<uint8_t*>(&ss) + ((sizeof(SharedStorage) + 15) & ~15);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -364,6 +370,7 @@ grouped_gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
     const int quad = warp & 3;
     const int col_half = (warp - FIRST_EPI_WARP) >> 2;
     const int row_in_tile = quad * 32 + lane;
+    const uint32_t my_stage = smem_u32(stage_out) + (warp - FIRST_EPI_WARP) * (32 * STAGE_OUT_PITCH);
     uint32_t acc_phase = 0;
     bool ok = true;
     Tile tile;
@@ -398,11 +405,14 @@ grouped_gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
           // of its row, so amax, scale and conversion are thread-local (same arithmetic as the row quantiser on the
           // bf16 dz: bit-identical bytes)
           done = true;
-          if (row_ok && cols_ok) {
+          if (cols_ok) {  // warp-uniform; rows past the expert's end read zeros and store nothing
             auto quantise_block = [&](uint32_t (&a)[32], uint32_t (&b)[32], int n) {
               float amax = 0.f;
-              dswiglu_chunk<true>(p, r, n, a, score, ds_acc, amax);
-              dswiglu_chunk<true>(p, r, n + 32, b, score, ds_acc, amax);
+              dswiglu_chunk_staged<true, STAGE_OUT_PITCH>(p, my_stage, lane, r - lane, tile.row_end, n, a, score, ds_acc,
+                                                          amax);
+              dswiglu_chunk_staged<true, STAGE_OUT_PITCH>(p, my_stage, lane, r - lane, tile.row_end, n + 32, b, score,
+                                                          ds_acc, amax);
+              if (!row_ok) return;
               float inv;
               const uint8_t byte = fp8::pow2_scale(amax, inv);
               uint8_t* dst = p.q_out + static_cast<long long>(r) * (2ll * p.N) + 2 * n;
@@ -439,15 +449,11 @@ grouped_gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
           float amax = 0.f;
           auto swiglu_keep = [&](uint32_t (&a)[32], int c) {
             const int n = ncol0 + 32 * c;
-            if (row_ok && cols_ok && p.out0 != nullptr) {
-              __nv_bfloat16* zdst = p.out0 + r * p.ld0 + n;
+            if (cols_ok && p.out0 != nullptr) {  // warp-uniform: z leaves as 64-byte row segments
+              uint32_t zp[16];
 #pragma unroll
-              for (int j = 0; j < 4; ++j)
-                reinterpret_cast<uint4*>(zdst)[j] =
-                    make_uint4(pack_bf16(__uint_as_float(a[8 * j]), __uint_as_float(a[8 * j + 1])),
-                               pack_bf16(__uint_as_float(a[8 * j + 2]), __uint_as_float(a[8 * j + 3])),
-                               pack_bf16(__uint_as_float(a[8 * j + 4]), __uint_as_float(a[8 * j + 5])),
-                               pack_bf16(__uint_as_float(a[8 * j + 6]), __uint_as_float(a[8 * j + 7])));
+              for (int j = 0; j < 16; ++j) zp[j] = pack_bf16(__uint_as_float(a[2 * j]), __uint_as_float(a[2 * j + 1]));
+              warp_store_rows64<STAGE_OUT_PITCH>(my_stage, lane, zp, p.out0, p.ld0, r - lane, tile.row_end, n);
             }
 #pragma unroll
             for (int j = 0; j < 8; ++j) {  // gate = even column, up = odd column
@@ -485,6 +491,33 @@ grouped_gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
                                                             cvt4(yw[8 * j + 4], yw[8 * j + 5]), cvt4(yw[8 * j + 6], yw[8 * j + 7]));
             if (col_half == 0) p.q_scale[static_cast<long long>(r) * p.q_scale_ld + tile.n0 / BN] = byte;
           }
+        }
+      }
+      if constexpr (EPI == EPI_DSWIGLU) {
+        if (!done && cols_ok) {
+          done = true;
+          float unused = 0.f;
+          dswiglu_chunk_staged<false, STAGE_OUT_PITCH>(p, my_stage, lane, r - lane, tile.row_end, ncol0, v0, score, ds_acc, unused);
+          dswiglu_chunk_staged<false, STAGE_OUT_PITCH>(p, my_stage, lane, r - lane, tile.row_end, ncol0 + 32, v1, score, ds_acc, unused);
+          if (ncol0 + 64 < p.N) {
+            dswiglu_chunk_staged<false, STAGE_OUT_PITCH>(p, my_stage, lane, r - lane, tile.row_end, ncol0 + 64, v2, score, ds_acc, unused);
+            dswiglu_chunk_staged<false, STAGE_OUT_PITCH>(p, my_stage, lane, r - lane, tile.row_end, ncol0 + 96, v3, score, ds_acc, unused);
+          }
+        }
+      }
+      if constexpr (EPI == EPI_STORE) {
+        if (cols_ok) {  // warp-uniform
+          done = true;
+          auto store32 = [&](uint32_t (&a)[32], int n) {
+            uint32_t w[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) w[j] = pack_bf16(__uint_as_float(a[2 * j]), __uint_as_float(a[2 * j + 1]));
+            warp_store_rows64<STAGE_OUT_PITCH>(my_stage, lane, w, p.out0, p.ld0, r - lane, tile.row_end, n);
+          };
+          store32(v0, ncol0);
+          store32(v1, ncol0 + 32);
+          store32(v2, ncol0 + 64);
+          store32(v3, ncol0 + 96);
         }
       }
       if (!done && row_ok && cols_ok) {

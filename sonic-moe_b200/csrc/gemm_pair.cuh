@@ -149,65 +149,6 @@ __device__ __forceinline__ int unit_num_kb(const GemmParams& p, long long t, lon
   }
 }
 
-// Warp-cooperative row I/O through a warp's staging rows (32 rows of PITCH bytes).  Lane l owns row l of a 32-row
-// block; global memory is touched with consecutive lanes on consecutive 16-byte pieces of one row, so an instruction
-// moves whole 64- or 128-byte row segments.  Rows at or beyond row_end are skipped.  Every lane must call.
-template <int PITCH>
-__device__ __forceinline__ void warp_store_rows64(uint32_t stage, int lane, const uint32_t (&w)[16], __nv_bfloat16* out,
-                                                  long long ld, int row_base, int row_end, int col) {
-#pragma unroll
-  for (int q = 0; q < 4; ++q) st_shared_v4(stage + lane * PITCH + 16 * q, w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
-  __syncwarp();
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const int rr = 8 * i + (lane >> 2);
-    const uint4 v = ld_shared_v4(stage + rr * PITCH + 16 * (lane & 3));
-    if (row_base + rr < row_end) *reinterpret_cast<uint4*>(out + (row_base + rr) * ld + col + 8 * (lane & 3)) = v;
-  }
-  __syncwarp();
-}
-
-template <int PITCH>
-__device__ __forceinline__ void warp_store_rows128(uint32_t stage, int lane, const uint32_t (&w)[32], __nv_bfloat16* out,
-                                                   long long ld, int row_base, int row_end, int col) {
-  static_assert(PITCH >= 128 + 16, "128-byte payload");
-#pragma unroll
-  for (int q = 0; q < 8; ++q) st_shared_v4(stage + lane * PITCH + 16 * q, w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
-  __syncwarp();
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    const int rr = 4 * i + (lane >> 3);
-    const uint4 v = ld_shared_v4(stage + rr * PITCH + 16 * (lane & 7));
-    if (row_base + rr < row_end) *reinterpret_cast<uint4*>(out + (row_base + rr) * ld + col + 8 * (lane & 7)) = v;
-  }
-  __syncwarp();
-}
-
-// The inverse: 32 rows x 128 bytes read with whole-row-segment loads; lane l ends with row l (zeros past row_end).
-template <int PITCH>
-__device__ __forceinline__ void warp_load_rows128(uint32_t stage, int lane, uint32_t (&w)[32], const __nv_bfloat16* src,
-                                                  long long ld, int row_base, int row_end, int col) {
-  static_assert(PITCH >= 128 + 16, "128-byte payload");
-  uint4 v[8];
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    const int rr = 4 * i + (lane >> 3);
-    v[i] = make_uint4(0u, 0u, 0u, 0u);
-    if (row_base + rr < row_end)
-      v[i] = *reinterpret_cast<const uint4*>(src + (row_base + rr) * ld + col + 8 * (lane & 7));
-  }
-#pragma unroll
-  for (int i = 0; i < 8; ++i)
-    st_shared_v4(stage + (4 * i + (lane >> 3)) * PITCH + 16 * (lane & 7), v[i].x, v[i].y, v[i].z, v[i].w);
-  __syncwarp();
-#pragma unroll
-  for (int q = 0; q < 8; ++q) {
-    const uint4 t = ld_shared_v4(stage + lane * PITCH + 16 * q);
-    w[4 * q] = t.x; w[4 * q + 1] = t.y; w[4 * q + 2] = t.z; w[4 * q + 3] = t.w;
-  }
-  __syncwarp();
-}
-
 template <bool RAGGED_K, bool A_GATHER, bool A_MN, bool B_GATHER, bool B_MN, int EPI, int EW, int GW,
           int DUAL = DUAL_NONE>
 __global__ void __launch_bounds__(threads(EW, GW, DUAL != 0), 1)
