@@ -226,13 +226,15 @@ class CudaOps:
         route.token_offset = fn._sorted_offsets(tokens, R)
         return route
 
-    def local_layer(self, x_rows, w1, w2, scores, tokens, experts, num_local_experts, inference):
+    def local_layer(self, x_rows, w1, w2, scores, tokens, experts, num_local_experts, inference, on_dx=None):
         """out[r] = sum over the pairs (r, e) of score * expert_e(x_rows[r]); w1 (E_l,2I,H), w2 (E_l,H,I);
-        ``tokens`` ascending."""
+        ``tokens`` ascending.  ``on_dx``: called in the backward pass with the gradient of x_rows as soon as it
+        exists, before the weight-gradient GEMMs are launched."""
         from . import functional as fn
 
         R = x_rows.shape[0]
         route = self._route(tokens, experts, num_local_experts, R)
+        route.on_dx = on_dx
         return fn._RoutedExperts.apply(x_rows, w1.permute(1, 2, 0), w2.permute(1, 2, 0), scores, route, R, inference)
 
 
@@ -243,7 +245,7 @@ class Fp8CudaOps(CudaOps):
     def __init__(self, scale_format: str | None = None):
         self.scale_format = scale_format
 
-    def local_layer(self, x_rows, w1, w2, scores, tokens, experts, num_local_experts, inference):
+    def local_layer(self, x_rows, w1, w2, scores, tokens, experts, num_local_experts, inference, on_dx=None):
         from .functional.fp8 import _RoutedExpertsFp8
 
         R = x_rows.shape[0]
@@ -340,22 +342,49 @@ class _Lease:
         self.transport.release_slot(self.slot)
 
 
+class _EarlyReturn:
+    """Sends the gradient of the dispatched rows back to the tokens' ranks as soon as the local experts' backward
+    pass has produced it: copy-engine copies and the barrier on the transport's copy stream, while the compute
+    stream goes on with the two weight-gradient GEMMs, which nothing downstream waits for.  `start` is what the
+    local layer calls (`on_dx`); `_PeerDispatch.backward` then only waits for the event."""
+
+    def __init__(self, transport, plan, tag):
+        self.transport, self.plan, self.tag = transport, plan, tag
+        self.dx = self.landed = self.view = None
+
+    def start(self, dx):
+        tr, plan = self.transport, self.plan
+        self.dx = dx
+        self.landed, self.view = tr.send_async(dx, plan.recv_rows, plan.return_offset, sum(plan.send_rows),
+                                               ("return_bwd", self.tag), plan.token_capacity)
+
+
 class _PeerDispatch(torch.autograd.Function):
     """x (T,H) -> the rows this rank's experts need, written by their owners straight into this rank's exchange
     buffer (gather fused with the send); backward: the row gradients go back and each token's are added up."""
 
     @staticmethod
-    def forward(ctx, x, plan, transport, keep, slot, tag):
+    def forward(ctx, x, plan, transport, keep, slot, tag, early):
         if keep:
             ctx.lease = _Lease(transport, slot)
-        ctx.plan, ctx.transport, ctx.T, ctx.tag = plan, transport, x.shape[0], tag
+        ctx.plan, ctx.transport, ctx.T, ctx.tag, ctx.early = plan, transport, x.shape[0], tag, early
         return _timed_exchange(lambda: transport.dispatch_rows(x, plan, ("dispatch_fwd", slot, tag)), True)
 
     @staticmethod
     def backward(ctx, g):
-        back = _timed_exchange(lambda: ctx.transport.return_rows(g, ctx.plan, ("return_bwd", ctx.tag)), True)
+        early = ctx.early
+        if early is not None and early.landed is not None:
+            # the rows left while the weight-gradient GEMMs ran (every rank takes this branch or none does: whether
+            # the local layer called the hook does not depend on the data)
+            if g.data_ptr() != early.dx.data_ptr():
+                raise RuntimeError("the gradient handed to the dispatch is not the tensor the local layer announced")
+            ctx.transport.compute_wait(early.landed)
+            back = early.view
+            early.dx = None
+        else:
+            back = _timed_exchange(lambda: ctx.transport.return_rows(g, ctx.plan, ("return_bwd", ctx.tag)), True)
         ctx.lease = None
-        return _sum_rows(back, ctx.plan.rows, ctx.T), None, None, None, None, None
+        return _sum_rows(back, ctx.plan.rows, ctx.T), None, None, None, None, None, None
 
 
 class _PeerCombine(torch.autograd.Function):
@@ -376,23 +405,28 @@ class _PeerCombine(torch.autograd.Function):
 
 class PeerMemoryTransport:
     """Token rows through buffers the ranks map from each other (sonicmoe/peer.py): the library's own kernels and
-    copy-engine copies over NVLink instead of an NCCL all-to-all, every exchange in order on the caller's stream.
-    bf16 CUDA rows, one node."""
+    copy-engine copies over NVLink instead of an NCCL all-to-all.  Every exchange runs in order on the caller's
+    stream, except the return of the row gradients in the backward pass, which travels on a copy stream while the
+    weight-gradient GEMMs run (`_EarlyReturn`).  bf16 CUDA rows, one node."""
 
     micro_batches = 1
 
     def __init__(self, group, device, depth: int = 2):
-        from .peer import PeerTransport
+        from .peer import AsyncPeerTransport
 
-        self.impl = PeerTransport(group, device, depth)
+        self.impl = AsyncPeerTransport(group, device, depth)
 
     def dispatch_start(self, x, plan, keep, tag):
         if tag == 0:
             self._slot = self.impl.take_slot(keep)
-        return _PeerDispatch.apply(x, plan, self.impl, keep and tag == 0, self._slot, tag)
+        early = _EarlyReturn(self.impl, plan, tag) if keep else None
+        return _PeerDispatch.apply(x, plan, self.impl, keep and tag == 0, self._slot, tag, early), early
 
     def dispatch_wait(self, handle):
-        return handle
+        return handle[0]
+
+    def dx_hook(self, handle):
+        return None if handle[1] is None else handle[1].start
 
     def combine_start(self, rows, plan, tag):
         return (rows, tag)
@@ -636,7 +670,11 @@ def moe_ep_softmax_topk_layer(x, router_w, w1_local, w2_local, K, num_experts, g
     for c, plan in enumerate(plans):
         x_recv = transport.dispatch_wait(flights[c])
         s_recv, tokens, experts = routed[c]
-        o_recv = ops.local_layer(x_recv, w1_local, w2_local, s_recv, tokens, experts, e_local, inference)
+        hook = transport.dx_hook(flights[c]) if hasattr(transport, "dx_hook") else None
+        if hook is not None:
+            o_recv = ops.local_layer(x_recv, w1_local, w2_local, s_recv, tokens, experts, e_local, inference, on_dx=hook)
+        else:
+            o_recv = ops.local_layer(x_recv, w1_local, w2_local, s_recv, tokens, experts, e_local, inference)
         returning.append(transport.combine_start(o_recv, plan, c))
     outs = [transport.combine_finish(returning[c], plans[c], bounds[c + 1] - bounds[c]) for c in range(M)]
     o = outs[0] if M == 1 else torch.cat(outs)

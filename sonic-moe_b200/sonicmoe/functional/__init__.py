@@ -89,6 +89,9 @@ class Route:
     s_reverse_scatter_idx: torch.Tensor    # (TK,)  grouped row of each flat slot
     token_offset: torch.Tensor | None      # (T+1,) first flat slot of each token; None = fixed K per token
     K: int                                 # experts per token when token_offset is None
+    # called in the backward pass with dx as soon as it exists (before the weight-gradient GEMMs are launched): an
+    # expert-parallel caller starts sending dx back to the tokens' ranks while those GEMMs run
+    on_dx: object = None
 
 
 def _one_row_per_token(route: "Route", T: int) -> bool:
@@ -421,15 +424,8 @@ class _RoutedExperts(torch.autograd.Function):
             ds = torch.empty_like(scores_flat)
             check(lib.smoe_ds_reduce(ds_partial.data_ptr(), route.s_scatter_idx.data_ptr(), ds.data_ptr(),
                                      _lib.dtype_code(ds.dtype), TK, ncols, stream), "ds_reduce")
-            dw2 = torch.empty_like(w2e)
-            check(lib.smoe_down_projection_weight_grad(
-                dout.data_ptr(), y1s.data_ptr(), dw2.data_ptr(), off, gat, T, H, I, E, TK, st.status.data_ptr(),
-                stream), "down_projection_weight_grad")
-            del y1s, ds_partial
-            dw1 = torch.empty_like(w1e)
-            check(lib.smoe_up_projection_weight_grad(
-                x.data_ptr(), dz.data_ptr(), dw1.data_ptr(), off, gat, T, H, I, E, TK, st.status.data_ptr(), stream),
-                "up_projection_weight_grad")
+            # dX first: nothing else depends on the weight gradients, and a caller that has to send dx somewhere
+            # (expert parallelism) can do so while the two weight-gradient GEMMs run
             dx = torch.empty(T, H, dtype=x.dtype, device=dev)
             if _one_row_per_token(route, T):
                 check(lib.smoe_up_projection_backward_dx_rows(
@@ -444,6 +440,18 @@ class _RoutedExperts(torch.autograd.Function):
                     dx_expanded.data_ptr(), dx.data_ptr(), None, _lib.SMOE_F32,
                     route.s_reverse_scatter_idx.data_ptr(), ptr(route.token_offset), T, H, max(route.K, 1), stream),
                     "gather_sum")
+                del dx_expanded
+            if route.on_dx is not None:
+                route.on_dx(dx)
+            dw2 = torch.empty_like(w2e)
+            check(lib.smoe_down_projection_weight_grad(
+                dout.data_ptr(), y1s.data_ptr(), dw2.data_ptr(), off, gat, T, H, I, E, TK, st.status.data_ptr(),
+                stream), "down_projection_weight_grad")
+            del y1s, ds_partial
+            dw1 = torch.empty_like(w1e)
+            check(lib.smoe_up_projection_weight_grad(
+                x.data_ptr(), dz.data_ptr(), dw1.data_ptr(), off, gat, T, H, I, E, TK, st.status.data_ptr(), stream),
+                "up_projection_weight_grad")
         # gradients in the layout of the (out, in, E) views the caller passed
         return dx, dw1.permute(1, 2, 0), dw2.permute(1, 2, 0), ds, None, None, None
 
