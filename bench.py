@@ -835,6 +835,9 @@ def run_ep_arm(args, rank, world, local_rank, workload):
                            "memory and o and dx back to it (per rank)"},
             "gpu_launches": launches,
             "all_to_all_ms_per_step": a2a.item(), "all_to_all_share": a2a.item() / ms_per_step,
+            "all_to_all_note": "sum of the exchanges' durations on the streams they run on (CUDA events, max over ranks); "
+                               "with the peer transport the backward return of the row gradients runs on the copy stream "
+                               "beside the weight-gradient GEMMs, so part of this time is not exposed",
             "expert_load_max_over_mean": (freq.max() / freq.mean()).item(),
             "rank_load_max_over_mean": (per_rank_rows.max() / per_rank_rows.mean()).item(),
             "ep_parity": parity,
