@@ -199,6 +199,19 @@ int smoe_up_projection_weight_grad(const void* x, const void* dz, void* dw1, con
                                    const int* x_gather_idx, int T, int H, int I, int E, int TK, int* status,
                                    void* stream);
 
+/* The two weight gradients added to what dw2 / dw1 already hold: dW += (the chunk's gradient rounded to bf16),
+ * added in fp32 and rounded to bf16.  An expert without rows, and TK == 0, leave the buffer untouched.
+ * A batch whose rows arrive in several chunks (the micro-batches of the expert-parallel exchange) stores the first
+ * chunk with the calls above and adds the later ones here.  That is the accumulation autograd performs for a
+ * weight used twice, without its extra read-add-write pass over both gradient tensors (the reference's kernels
+ * write the gradient of the whole batch at once: sonicmoe/functional/backward.py:237-257, 438-458). */
+int smoe_down_projection_weight_grad_accumulate(const void* dout, const void* y1s, void* dw2,
+                                                const int* expert_offset, const int* x_gather_idx, int T, int H, int I,
+                                                int E, int TK, int* status, void* stream);
+int smoe_up_projection_weight_grad_accumulate(const void* x, const void* dz, void* dw1, const int* expert_offset,
+                                              const int* x_gather_idx, int T, int H, int I, int E, int TK, int* status,
+                                              void* stream);
+
 /* ---------------------------------------------------------------------------------------------
  * Any activation of the layer, and expert biases.  Activation codes: 0 swiglu, 1 geglu, 2 reglu (gated:
  * W1[e] has 2I rows, gate row 2j / up row 2j+1), 3 relu_sq, 4 relu, 5 gelu (erf), 6 silu (W1[e] has I rows).

@@ -51,6 +51,8 @@ struct GemmParams {
   float* ds_partial;        // (2 * ceil(N/BN), total_rows) fp32: one row of partials per 128 accumulator columns
   float* acc_out;           // EPI_SCATTER: (gather_rows, N) fp32
   int* status;              // device word, 0 = ok
+  int accumulate;           // plain-store epilogues: add to what out0 holds (bf16, fp32 sum, one rounding) instead of
+                            // overwriting it -- weight gradients summed over several chunks of tokens
   // general epilogues
   const __nv_bfloat16* bias;  // (E, N) added to the accumulator, or nullptr
   int act;                    // Activation code
@@ -186,6 +188,20 @@ __device__ __forceinline__ void warp_load_rows128(uint32_t stage, int lane, uint
     w[4 * q] = t.x; w[4 * q + 1] = t.y; w[4 * q + 2] = t.z; w[4 * q + 3] = t.w;
   }
   __syncwarp();
+}
+
+// eight packed bf16 values plus the eight at dst (fp32 sums, rounded once)
+__device__ __forceinline__ uint4 add_bf16x8(uint4 a, const uint4* dst) {
+  const uint4 b = *dst;
+  const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
+  uint32_t o[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 x = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&aw[i]));
+    const float2 y = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&bw[i]));
+    o[i] = pack_bf16(x.x + y.x, x.y + y.y);
+  }
+  return make_uint4(o[0], o[1], o[2], o[3]);
 }
 
 // acc (+ bias) as 32 floats
@@ -330,7 +346,8 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, int expert, 
       w.y = pack_bf16(__uint_as_float(v[8 * j + 2]), __uint_as_float(v[8 * j + 3]));
       w.z = pack_bf16(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5]));
       w.w = pack_bf16(__uint_as_float(v[8 * j + 6]), __uint_as_float(v[8 * j + 7]));
-      reinterpret_cast<uint4*>(dst)[j] = w;
+      uint4* d4 = reinterpret_cast<uint4*>(dst) + j;
+      *d4 = p.accumulate ? add_bf16x8(w, d4) : w;
     }
   } else if constexpr (EPI == EPI_SWIGLU) {
     if (p.out0 != nullptr) {

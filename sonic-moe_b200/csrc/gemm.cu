@@ -334,11 +334,12 @@ int smoe_up_projection_backward_dx_rows(const void* dz, const void* w1, void* dx
   return launch<false, false, false, false, true, EPI_STORE_ROWS>(tmA, tmB, p, static_cast<cudaStream_t>(stream));
 }
 
-int smoe_down_projection_weight_grad(const void* dout, const void* y1s, void* dw2, const int* expert_offset,
-                                     const int* x_gather_idx, int T, int H, int I, int E, int TK, int* status,
-                                     void* stream) {
+static int down_weight_grad(const void* dout, const void* y1s, void* dw2, const int* expert_offset,
+                            const int* x_gather_idx, int T, int H, int I, int E, int TK, int* status, void* stream,
+                            int accumulate) {
   if (bad_shape(H, I, E) || bad_tokens(T, TK)) return SMOE_ERR_SHAPE;
   if (TK == 0) {
+    if (accumulate) return SMOE_OK;
     return cudaMemsetAsync(dw2, 0, (size_t)E * H * I * 2, static_cast<cudaStream_t>(stream)) == cudaSuccess
                ? SMOE_OK : SMOE_ERR_LAUNCH;
   }
@@ -349,15 +350,15 @@ int smoe_down_projection_weight_grad(const void* dout, const void* y1s, void* dw
   p.E = E; p.M = H; p.N = I; p.total_rows = TK; p.gather_rows = T;
   p.off = expert_offset; p.gather = x_gather_idx;
   p.out0 = static_cast<__nv_bfloat16*>(dw2); p.ld0 = I; p.out0_expert_stride = (long long)H * I;
-  p.status = status;
+  p.status = status; p.accumulate = accumulate;
   return launch<true, true, true, false, true, EPI_STORE>(tmA, tmB, p, static_cast<cudaStream_t>(stream));
 }
 
-int smoe_up_projection_weight_grad(const void* x, const void* dz, void* dw1, const int* expert_offset,
-                                   const int* x_gather_idx, int T, int H, int I, int E, int TK, int* status,
-                                   void* stream) {
+static int up_weight_grad(const void* x, const void* dz, void* dw1, const int* expert_offset, const int* x_gather_idx,
+                          int T, int H, int I, int E, int TK, int* status, void* stream, int accumulate) {
   if (bad_shape(H, I, E) || bad_tokens(T, TK)) return SMOE_ERR_SHAPE;
   if (TK == 0) {
+    if (accumulate) return SMOE_OK;
     return cudaMemsetAsync(dw1, 0, (size_t)E * 2 * I * H * 2, static_cast<cudaStream_t>(stream)) == cudaSuccess
                ? SMOE_OK : SMOE_ERR_LAUNCH;
   }
@@ -368,8 +369,32 @@ int smoe_up_projection_weight_grad(const void* x, const void* dz, void* dw1, con
   p.E = E; p.M = 2 * I; p.N = H; p.total_rows = TK; p.gather_rows = T;
   p.off = expert_offset; p.gather = x_gather_idx;
   p.out0 = static_cast<__nv_bfloat16*>(dw1); p.ld0 = H; p.out0_expert_stride = (long long)2 * I * H;
-  p.status = status;
+  p.status = status; p.accumulate = accumulate;
   return launch<true, false, true, true, true, EPI_STORE>(tmA, tmB, p, static_cast<cudaStream_t>(stream));
+}
+
+int smoe_down_projection_weight_grad(const void* dout, const void* y1s, void* dw2, const int* expert_offset,
+                                     const int* x_gather_idx, int T, int H, int I, int E, int TK, int* status,
+                                     void* stream) {
+  return down_weight_grad(dout, y1s, dw2, expert_offset, x_gather_idx, T, H, I, E, TK, status, stream, 0);
+}
+
+int smoe_down_projection_weight_grad_accumulate(const void* dout, const void* y1s, void* dw2,
+                                                const int* expert_offset, const int* x_gather_idx, int T, int H, int I,
+                                                int E, int TK, int* status, void* stream) {
+  return down_weight_grad(dout, y1s, dw2, expert_offset, x_gather_idx, T, H, I, E, TK, status, stream, 1);
+}
+
+int smoe_up_projection_weight_grad(const void* x, const void* dz, void* dw1, const int* expert_offset,
+                                   const int* x_gather_idx, int T, int H, int I, int E, int TK, int* status,
+                                   void* stream) {
+  return up_weight_grad(x, dz, dw1, expert_offset, x_gather_idx, T, H, I, E, TK, status, stream, 0);
+}
+
+int smoe_up_projection_weight_grad_accumulate(const void* x, const void* dz, void* dw1, const int* expert_offset,
+                                              const int* x_gather_idx, int T, int H, int I, int E, int TK, int* status,
+                                              void* stream) {
+  return up_weight_grad(x, dz, dw1, expert_offset, x_gather_idx, T, H, I, E, TK, status, stream, 1);
 }
 
 }  // extern "C"

@@ -517,7 +517,10 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
                 const int rr = 8 * i + (lane >> 2);
                 const uint4 w = ld_shared_v4(my_stage + rr * STAGE_OUT_PITCH_NARROW + 16 * (lane & 3));
                 const int r = row_base + rr;
-                if (r < tile.row_end) *reinterpret_cast<uint4*>(out + r * p.ld0 + n + 8 * (lane & 3)) = w;
+                if (r < tile.row_end) {
+                  uint4* dst = reinterpret_cast<uint4*>(out + r * p.ld0 + n + 8 * (lane & 3));
+                  *dst = p.accumulate ? add_bf16x8(w, dst) : w;
+                }
               }
               __syncwarp();
             }
@@ -683,7 +686,10 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
               const int rr = 4 * i + (lane >> 3);
               const uint4 w = ld_shared_v4(my_stage + rr * STAGE_OUT_PITCH_WIDE + 16 * (lane & 7));
               const int rw = row_base + rr;
-              if (rw < tile.row_end) *reinterpret_cast<uint4*>(out + rw * p.ld0 + n + 8 * (lane & 7)) = w;
+              if (rw < tile.row_end) {
+                uint4* dst = reinterpret_cast<uint4*>(out + rw * p.ld0 + n + 8 * (lane & 7));
+                *dst = p.accumulate ? add_bf16x8(w, dst) : w;
+              }
             }
             __syncwarp();
           }

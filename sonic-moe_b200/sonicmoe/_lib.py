@@ -59,6 +59,8 @@ SIGNATURES: dict[str, tuple] = {
     "smoe_up_projection_backward_dx": (I, [P, P, P, P, I, I, I, I, P, P]),
     "smoe_down_projection_weight_grad": (I, [P, P, P, P, P, I, I, I, I, I, P, P]),
     "smoe_up_projection_weight_grad": (I, [P, P, P, P, P, I, I, I, I, I, P, P]),
+    "smoe_down_projection_weight_grad_accumulate": (I, [P, P, P, P, P, I, I, I, I, I, P, P]),
+    "smoe_up_projection_weight_grad_accumulate": (I, [P, P, P, P, P, I, I, I, I, I, P, P]),
     "smoe_up_projection_forward_act": (I, [P, P, P, P, P, P, P, I, I, I, I, I, I, P, P]),
     "smoe_down_projection_forward_bias": (I, [P, P, P, P, P, I, I, I, I, P, P]),
     "smoe_down_projection_backward_dact": (I, [P, P, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, P, P]),

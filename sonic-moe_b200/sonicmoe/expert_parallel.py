@@ -208,6 +208,9 @@ def received_pair_tokens(pair_row: torch.Tensor, recv_rows: list[int], recv_pair
 class CudaOps:
     """The device operations of the expert-parallel layer on the library's CUDA kernels."""
 
+    # the chunks of one batch add their weight gradients into one pair of buffers inside the GEMM epilogues
+    shares_weight_grads = True
+
     def topk_softmax(self, logits, K):
         from . import functional as fn
 
@@ -226,15 +229,17 @@ class CudaOps:
         route.token_offset = fn._sorted_offsets(tokens, R)
         return route
 
-    def local_layer(self, x_rows, w1, w2, scores, tokens, experts, num_local_experts, inference, on_dx=None):
+    def local_layer(self, x_rows, w1, w2, scores, tokens, experts, num_local_experts, inference, on_dx=None,
+                    wgrad_sum=None):
         """out[r] = sum over the pairs (r, e) of score * expert_e(x_rows[r]); w1 (E_l,2I,H), w2 (E_l,H,I);
         ``tokens`` ascending.  ``on_dx``: called in the backward pass with the gradient of x_rows as soon as it
-        exists, before the weight-gradient GEMMs are launched."""
+        exists, before the weight-gradient GEMMs are launched.  ``wgrad_sum``: the `functional.WeightGradSum` the
+        chunks of one batch share."""
         from . import functional as fn
 
         R = x_rows.shape[0]
         route = self._route(tokens, experts, num_local_experts, R)
-        route.on_dx = on_dx
+        route.on_dx, route.wgrad_sum = on_dx, wgrad_sum
         return fn._RoutedExperts.apply(x_rows, w1.permute(1, 2, 0), w2.permute(1, 2, 0), scores, route, R, inference)
 
 
@@ -242,10 +247,13 @@ class Fp8CudaOps(CudaOps):
     """As CudaOps, with the local experts' forward and activation-gradient GEMMs in FP8 (E4M3, block scales;
     ``scale_format`` "fp32", "ue8m0" or None for the FP8 module's default)."""
 
+    shares_weight_grads = False
+
     def __init__(self, scale_format: str | None = None):
         self.scale_format = scale_format
 
-    def local_layer(self, x_rows, w1, w2, scores, tokens, experts, num_local_experts, inference, on_dx=None):
+    def local_layer(self, x_rows, w1, w2, scores, tokens, experts, num_local_experts, inference, on_dx=None,
+                    wgrad_sum=None):
         from .functional.fp8 import _RoutedExpertsFp8
 
         R = x_rows.shape[0]
@@ -446,6 +454,8 @@ class _Flight:
         self.landed = None       # forward: the rows are in this rank's buffer (recorded on the copy stream)
         self.grad_ready = None   # backward: the gradient rows to send have been produced (compute stream)
         self.grad_landed = None  # backward: the gradient rows are in this rank's buffer (copy stream)
+        self.early_dx = None     # backward: the gradient tensor whose return the local layer's hook already started
+        self.early_landed = self.early_view = None
 
 
 class _DispatchStart(torch.autograd.Function):
@@ -465,9 +475,16 @@ class _DispatchStart(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, g):
-        tr, plan = ctx.transport, ctx.plan
-        landed, back = tr.send_async(g, plan.recv_rows, plan.return_offset, sum(plan.send_rows),
-                                     ("return_bwd", ctx.tag), plan.token_capacity, after=ctx.flight.grad_ready)
+        tr, plan, flight = ctx.transport, ctx.plan, ctx.flight
+        if flight.early_landed is not None:
+            # sent from the local layer's hook, while this chunk's weight-gradient GEMMs ran
+            if g.data_ptr() != flight.early_dx.data_ptr():
+                raise RuntimeError("the gradient handed to the dispatch is not the tensor the local layer announced")
+            landed, back = flight.early_landed, flight.early_view
+            flight.early_dx = None
+        else:
+            landed, back = tr.send_async(g, plan.recv_rows, plan.return_offset, sum(plan.send_rows),
+                                         ("return_bwd", ctx.tag), plan.token_capacity, after=flight.grad_ready)
         tr.compute_wait(landed)
         ctx.lease = None
         return _sum_rows(back, plan.rows, ctx.T), None, None, None, None, None, None
@@ -562,11 +579,24 @@ class PipelinedPeerTransport:
             self._slot = self.impl.take_slot(keep)
         flight = _Flight()
         view = _DispatchStart.apply(x, plan, self.impl, flight, keep and tag == 0, self._slot, tag)
-        return view, flight
+        return view, flight, (plan, tag) if keep else None
 
     def dispatch_wait(self, handle):
-        view, flight = handle
+        view, flight, _ = handle
         return _AfterLanding.apply(view, self.impl, flight)
+
+    def dx_hook(self, handle):
+        _, flight, going_back = handle
+        if going_back is None:
+            return None
+        plan, tag = going_back
+
+        def start(dx):
+            flight.early_dx = dx
+            flight.early_landed, flight.early_view = self.impl.send_async(
+                dx, plan.recv_rows, plan.return_offset, sum(plan.send_rows), ("return_bwd", tag), plan.token_capacity)
+
+        return start
 
     def combine_start(self, rows, plan, tag):
         flight = _Flight()
@@ -667,14 +697,18 @@ def moe_ep_softmax_topk_layer(x, router_w, w1_local, w2_local, K, num_experts, g
             experts = meta[:, 1].contiguous()
         routed.append((s_recv, tokens, experts))
     returning = []
+    extra = {}
+    if M > 1 and not inference and getattr(ops, "shares_weight_grads", False):
+        from .functional import WeightGradSum
+
+        extra["wgrad_sum"] = WeightGradSum(M)
     for c, plan in enumerate(plans):
         x_recv = transport.dispatch_wait(flights[c])
         s_recv, tokens, experts = routed[c]
         hook = transport.dx_hook(flights[c]) if hasattr(transport, "dx_hook") else None
         if hook is not None:
-            o_recv = ops.local_layer(x_recv, w1_local, w2_local, s_recv, tokens, experts, e_local, inference, on_dx=hook)
-        else:
-            o_recv = ops.local_layer(x_recv, w1_local, w2_local, s_recv, tokens, experts, e_local, inference)
+            extra["on_dx"] = hook
+        o_recv = ops.local_layer(x_recv, w1_local, w2_local, s_recv, tokens, experts, e_local, inference, **extra)
         returning.append(transport.combine_start(o_recv, plan, c))
     outs = [transport.combine_finish(returning[c], plans[c], bounds[c + 1] - bounds[c]) for c in range(M)]
     o = outs[0] if M == 1 else torch.cat(outs)

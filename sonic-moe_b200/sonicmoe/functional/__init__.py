@@ -92,6 +92,38 @@ class Route:
     # called in the backward pass with dx as soon as it exists (before the weight-gradient GEMMs are launched): an
     # expert-parallel caller starts sending dx back to the tokens' ranks while those GEMMs run
     on_dx: object = None
+    # shared by the chunks of one batch whose rows reach the same experts in several calls (`WeightGradSum`)
+    wgrad_sum: object = None
+
+
+class WeightGradSum:
+    """One pair of weight-gradient buffers for ``chunks`` calls of the routed experts on the same weights.
+
+    The first backward pass to run stores its dW1 / dW2, every later one adds to them inside the weight-gradient
+    GEMMs' epilogue (`smoe_*_weight_grad_accumulate`), and only the last returns gradients to autograd (the others
+    return None).  The result is what autograd's own accumulation of per-chunk bf16 gradients gives (bit for bit
+    with two chunks), without a full set of gradient tensors per chunk and the read-add-write pass that adds them.
+    Every chunk's backward pass has to run (all chunk outputs feed the loss)."""
+
+    def __init__(self, chunks: int):
+        self.remaining = chunks
+        self.dw1 = self.dw2 = None
+
+    def buffers(self, w1e, w2e):
+        """(dw1, dw2, accumulate?) for the chunk whose backward pass runs now."""
+        first = self.dw1 is None
+        if first:
+            self.dw1, self.dw2 = torch.empty_like(w1e), torch.empty_like(w2e)
+        return self.dw1, self.dw2, not first
+
+    def finish_chunk(self):
+        """The gradients if this was the last chunk, else (None, None)."""
+        self.remaining -= 1
+        if self.remaining > 0:
+            return None, None
+        dw1, dw2 = self.dw1, self.dw2
+        self.dw1 = self.dw2 = None
+        return dw1, dw2
 
 
 def _one_row_per_token(route: "Route", T: int) -> bool:
@@ -443,15 +475,22 @@ class _RoutedExperts(torch.autograd.Function):
                 del dx_expanded
             if route.on_dx is not None:
                 route.on_dx(dx)
-            dw2 = torch.empty_like(w2e)
-            check(lib.smoe_down_projection_weight_grad(
-                dout.data_ptr(), y1s.data_ptr(), dw2.data_ptr(), off, gat, T, H, I, E, TK, st.status.data_ptr(),
-                stream), "down_projection_weight_grad")
+            shared = route.wgrad_sum
+            if shared is None:
+                dw1, dw2, add = torch.empty_like(w1e), torch.empty_like(w2e), False
+            else:
+                dw1, dw2, add = shared.buffers(w1e, w2e)
+            down = lib.smoe_down_projection_weight_grad_accumulate if add else lib.smoe_down_projection_weight_grad
+            check(down(dout.data_ptr(), y1s.data_ptr(), dw2.data_ptr(), off, gat, T, H, I, E, TK,
+                       st.status.data_ptr(), stream), "down_projection_weight_grad")
             del y1s, ds_partial
-            dw1 = torch.empty_like(w1e)
-            check(lib.smoe_up_projection_weight_grad(
-                x.data_ptr(), dz.data_ptr(), dw1.data_ptr(), off, gat, T, H, I, E, TK, st.status.data_ptr(), stream),
-                "up_projection_weight_grad")
+            up = lib.smoe_up_projection_weight_grad_accumulate if add else lib.smoe_up_projection_weight_grad
+            check(up(x.data_ptr(), dz.data_ptr(), dw1.data_ptr(), off, gat, T, H, I, E, TK, st.status.data_ptr(),
+                     stream), "up_projection_weight_grad")
+            if shared is not None:
+                dw1, dw2 = shared.finish_chunk()
+                if dw1 is None:
+                    return dx, None, None, ds, None, None, None
         # gradients in the layout of the (out, in, E) views the caller passed
         return dx, dw1.permute(1, 2, 0), dw2.permute(1, 2, 0), ds, None, None, None
 

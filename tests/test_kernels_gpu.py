@@ -333,6 +333,45 @@ def test_backward_kernels(smoe, shape):
     assert st.item() == 0
 
 
+@pytest.mark.parametrize("shape", SHAPES)
+def test_weight_grad_accumulate_adds_to_buffer(smoe, shape):
+    """The accumulating forms add each chunk's bf16-rounded gradient to what the buffer holds (fp32 add, rounded to
+    bf16): bit-identical to `buffer + plain call`, the sum autograd forms for a weight used by two chunks.  Experts
+    without rows and TK = 0 leave the buffer as it was."""
+    _lib, _ = smoe
+    lib = _lib.lib
+    T, H, I, E, K, skew = shape
+    inp, f32, scores, route, fwd = _problem(*shape)
+    d = _dev(route)
+    TK = T * K
+    st = _lib.device_state(torch.device("cuda", 0)).status
+    stream = torch.cuda.current_stream().cuda_stream
+    x, dout = inp["x"].cuda(), inp["dout"].cuda()
+    g = torch.Generator(device="cuda").manual_seed(5)
+    dz = (torch.randn(TK, 2 * I, generator=g, device="cuda") * 0.1).bfloat16()
+    y1s = (torch.randn(TK, I, generator=g, device="cuda") * 0.1).bfloat16()
+    off_p, gat_p = d["expert_frequency_offset"].data_ptr(), d["x_gather_idx"].data_ptr()
+    for name, a, b, shape_w in (("down", dout, y1s, (E, H, I)), ("up", x, dz, (E, 2 * I, H))):
+        plain = getattr(lib, f"smoe_{name}_projection_weight_grad")
+        accum = getattr(lib, f"smoe_{name}_projection_weight_grad_accumulate")
+        one = torch.full(shape_w, float("nan"), dtype=torch.bfloat16, device="cuda")
+        assert plain(a.data_ptr(), b.data_ptr(), one.data_ptr(), off_p, gat_p, T, H, I, E, TK, st.data_ptr(),
+                     stream) == 0
+        base = (torch.randn(shape_w, generator=g, device="cuda") * one.float().std()).bfloat16()
+        buf = base.clone()
+        assert accum(a.data_ptr(), b.data_ptr(), buf.data_ptr(), off_p, gat_p, T, H, I, E, TK, st.data_ptr(),
+                     stream) == 0
+        assert torch.equal(buf, (base.float() + one.float()).bfloat16()), name
+        if skew:
+            assert torch.equal(buf[E - 1], base[E - 1])
+        zero_off = torch.zeros(E + 1, dtype=torch.int32, device="cuda")
+        assert accum(a.data_ptr(), b.data_ptr(), buf.data_ptr(), zero_off.data_ptr(), gat_p, T, H, I, E, 0,
+                     st.data_ptr(), stream) == 0
+        assert torch.equal(buf, (base.float() + one.float()).bfloat16())
+    torch.cuda.synchronize()
+    assert st.item() == 0
+
+
 def test_kernels_are_deterministic(smoe):
     """No atomics on the default path: two runs give identical bits."""
     _lib, _ = smoe
