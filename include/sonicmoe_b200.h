@@ -384,6 +384,16 @@ int smoe_peer_close(void* ptr);
 /* Stream-ordered copy of a contiguous segment between any two device buffers (local or mapped peer memory);
  * runs on a copy engine, leaves the multiprocessors to the GEMMs. */
 int smoe_peer_copy(void* dst, const void* src, size_t bytes, void* stream);
+/* Arrival flags without a kernel: the stream itself writes a 32-bit value to device memory of this GPU, or waits
+ * until each of `count` consecutive 32-bit words at addr is >= value (cyclic comparison, so a counter may wrap).
+ * A sender copies its data and then (same stream, smoe_peer_copy of 4 bytes) its exchange counter into the
+ * receiver's flag word; the receiver's stream waits on the words of all senders.  Neither side occupies a
+ * multiprocessor, so the hand-shake proceeds while persistent GEMM kernels hold every one of them (an NCCL
+ * barrier kernel would wait for a free multiprocessor and then keep it from the next GEMM).
+ * The reference has no multi-GPU path; these serve sonicmoe/expert_parallel.py of this library.
+ * Returns SMOE_ERR_DRIVER when the driver offers no stream memory operations. */
+int smoe_stream_write_value(void* addr, unsigned int value, void* stream);
+int smoe_stream_wait_values(const void* addr, int count, unsigned int value, void* stream);
 /* smoe_gather_sum whose output rows are cut into num_segments consecutive segments, each written to its own
  * destination: output row t of segment s (segment_start[s] <= t < segment_start[s+1]) goes to row
  * t - segment_start[s] of the (rows, H) bf16 buffer segment_ptr[s], which may be mapped peer memory (16-byte

@@ -3,16 +3,49 @@
 // (the dispatch of routed token rows and the return of per-token partial sums are fused with the row gather /
 // the reduction that produces them: no staging copy, every row crosses the link once), and copy-engine copies
 // for segments that are already contiguous.  Plain peer loads and stores only: no multicast of any kind.
+#include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <string.h>
+
+#include <mutex>
 
 #include "../../include/sonicmoe_b200.h"
 
 namespace smoe {
 
 static inline int rc_of(cudaError_t e) { return e == cudaSuccess ? SMOE_OK : SMOE_ERR_DRIVER; }
+
+// Stream memory operations of the driver (a 32-bit write / a wait for a 32-bit value, executed by the stream itself:
+// no kernel, no multiprocessor), resolved at run time so that the library links against the CUDA runtime only.
+using StreamWrite32Fn = CUresult (*)(CUstream, CUdeviceptr, cuuint32_t, unsigned int);
+using StreamWait32Fn = CUresult (*)(CUstream, CUdeviceptr, cuuint32_t, unsigned int);
+
+struct StreamMemOps {
+  StreamWrite32Fn write = nullptr;
+  StreamWait32Fn wait = nullptr;
+};
+
+static const StreamMemOps& stream_mem_ops() {
+  static StreamMemOps ops;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* w = nullptr;
+    void* q = nullptr;
+    cudaDriverEntryPointQueryResult rw, rq;
+    if (cudaGetDriverEntryPoint("cuStreamWriteValue32", &w, cudaEnableDefault, &rw) == cudaSuccess &&
+        rw == cudaDriverEntryPointSuccess &&
+        cudaGetDriverEntryPoint("cuStreamWaitValue32", &q, cudaEnableDefault, &rq) == cudaSuccess &&
+        rq == cudaDriverEntryPointSuccess) {
+      ops.write = reinterpret_cast<StreamWrite32Fn>(w);
+      ops.wait = reinterpret_cast<StreamWait32Fn>(q);
+    } else {
+      cudaGetLastError();
+    }
+  });
+  return ops;
+}
 
 struct PeerSegments {
   __nv_bfloat16* ptr[SMOE_MAX_PEERS];  // where segment s starts (in whichever GPU's memory)
@@ -116,6 +149,28 @@ int smoe_peer_copy(void* dst, const void* src, size_t bytes, void* stream) {
   if (bytes == 0) return SMOE_OK;
   if (dst == nullptr || src == nullptr) return SMOE_ERR_SHAPE;
   return rc_of(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDefault, static_cast<cudaStream_t>(stream)));
+}
+
+int smoe_stream_write_value(void* addr, unsigned int value, void* stream) {
+  if (addr == nullptr || (reinterpret_cast<uintptr_t>(addr) & 3u) != 0) return SMOE_ERR_ALIGNMENT;
+  const StreamMemOps& ops = stream_mem_ops();
+  if (ops.write == nullptr) return SMOE_ERR_DRIVER;
+  return ops.write(static_cast<CUstream>(stream), reinterpret_cast<CUdeviceptr>(addr), value,
+                   CU_STREAM_WRITE_VALUE_DEFAULT) == CUDA_SUCCESS ? SMOE_OK : SMOE_ERR_DRIVER;
+}
+
+int smoe_stream_wait_values(const void* addr, int count, unsigned int value, void* stream) {
+  if (count < 0) return SMOE_ERR_SHAPE;
+  if (count == 0) return SMOE_OK;
+  if (addr == nullptr || (reinterpret_cast<uintptr_t>(addr) & 3u) != 0) return SMOE_ERR_ALIGNMENT;
+  const StreamMemOps& ops = stream_mem_ops();
+  if (ops.wait == nullptr) return SMOE_ERR_DRIVER;
+  for (int i = 0; i < count; ++i) {
+    const CUdeviceptr a = reinterpret_cast<CUdeviceptr>(addr) + 4ull * static_cast<unsigned>(i);
+    if (ops.wait(static_cast<CUstream>(stream), a, value, CU_STREAM_WAIT_VALUE_GEQ) != CUDA_SUCCESS)
+      return SMOE_ERR_DRIVER;
+  }
+  return SMOE_OK;
 }
 
 int smoe_gather_sum_to_peers(const void* src, const void* weights, int weights_dtype, const int* reverse_idx,

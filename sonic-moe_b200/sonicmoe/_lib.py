@@ -8,7 +8,7 @@ from __future__ import annotations
 
 import ctypes
 import os
-from ctypes import c_int, c_longlong, c_size_t, c_void_p
+from ctypes import c_int, c_longlong, c_size_t, c_uint, c_void_p
 
 import torch
 
@@ -91,6 +91,8 @@ SIGNATURES: dict[str, tuple] = {
     "smoe_peer_open": (I, [P, P]),
     "smoe_peer_close": (I, [P]),
     "smoe_peer_copy": (I, [P, P, c_size_t, P]),
+    "smoe_stream_write_value": (I, [P, c_uint, P]),
+    "smoe_stream_wait_values": (I, [P, I, c_uint, P]),
     "smoe_gather_sum_to_peers": (I, [P, P, I, P, P, I, I, I, P, P, I, I, P]),
 }
 

@@ -22,6 +22,7 @@ bf16 rows whose length is a multiple of 8.
 from __future__ import annotations
 
 import ctypes
+import os
 
 import torch
 import torch.distributed as dist
@@ -212,6 +213,13 @@ class PeerTransport:
 exchange_events: list | None = None
 
 
+class _Arrived:
+    """Exchange number `seq` of a transport: its rows are here once every sender's flag word has reached `seq`."""
+
+    def __init__(self, seq: int):
+        self.seq = seq
+
+
 class AsyncPeerTransport(PeerTransport):
     """The peer transport with its copies on a second, high-priority stream: `send_async` returns at once with an
     event; whoever reads the received rows makes its stream wait for that event first.  Segments travel with
@@ -225,20 +233,54 @@ class AsyncPeerTransport(PeerTransport):
         self.barrier_group = dist.new_group(ranks=ranks, backend="nccl")
         with torch.cuda.device(device):
             self.comm = torch.cuda.Stream(device=device, priority=-1)
+        # Arrival flags: word p of `flags` on this rank = number of the last exchange whose rows from rank p have
+        # landed here.  Written by the senders' copy engines, waited for by this rank's streams: no kernel on either
+        # side.  Without stream memory operations (or SONICMOE_EP_BARRIER=nccl) every exchange ends with an
+        # all-reduce barrier on the copy stream instead.
+        self.seq = 0
+        self.counter = torch.zeros(1, dtype=torch.int32, device=device)
+        self.flags = None
+        ok = os.environ.get("SONICMOE_EP_BARRIER", "flags") == "flags" and self._stream_values_work()
+        verdict = torch.tensor([1 if ok else 0], dtype=torch.int32, device=device)
+        dist.all_reduce(verdict, op=dist.ReduceOp.MIN, group=group)
+        if verdict.item() == 1:
+            self.flags = PeerBuffer(1 << 16, group, device)
+
+    def _stream_values_work(self) -> bool:
+        with torch.cuda.device(self.device):
+            stream = self.comm.cuda_stream
+            ok = (lib.smoe_stream_write_value(self.counter.data_ptr(), 0, stream) == 0 and
+                  lib.smoe_stream_wait_values(self.counter.data_ptr(), 1, 0, stream) == 0)
+            self.comm.synchronize()
+        return ok
+
+    def close(self) -> None:
+        if self.flags is not None:
+            self.flags.close()
+            self.flags = None
+        super().close()
 
     def mark_compute(self) -> torch.cuda.Event:
         ev = torch.cuda.Event()
         ev.record(torch.cuda.current_stream(self.device))
         return ev
 
-    def compute_wait(self, ev: torch.cuda.Event) -> None:
-        torch.cuda.current_stream(self.device).wait_event(ev)
+    def compute_wait(self, landed) -> None:
+        """The current stream waits for what `send_async` returned: the rows of that exchange are in this rank's
+        buffer afterwards."""
+        if isinstance(landed, _Arrived):
+            with torch.cuda.device(self.device):
+                check(lib.smoe_stream_wait_values(self.flags.own_ptr, self.world, landed.seq, stream_ptr(self.device)),
+                      "stream_wait_values")
+        else:
+            torch.cuda.current_stream(self.device).wait_event(landed)
 
     def send_async(self, src: torch.Tensor, seg_rows: list[int], dst_offsets: list[int], n_recv: int, key: tuple,
                    token_capacity: int, after: torch.cuda.Event | None = None):
         """Segment d of `src` (seg_rows[d] consecutive rows) goes to row dst_offsets[d] of rank d's buffer `key`, once
-        `after` (default: everything issued so far on the current stream) has happened.  Returns (event recorded
-        on the copy stream after the exchange's barrier, this rank's first n_recv rows of the buffer)."""
+        `after` (default: everything issued so far on the current stream) has happened.  Returns (what to hand to
+        `compute_wait` before reading, this rank's first n_recv rows of the buffer).  Every rank calls this the same
+        number of times in the same order (the exchanges are numbered)."""
         _lib.require_cuda(src, "rows")
         src = src.contiguous()
         H = src.shape[1]
@@ -257,16 +299,25 @@ class AsyncPeerTransport(PeerTransport):
             starts = [0]
             for d in range(W):
                 starts.append(starts[-1] + seg_rows[d])
+            if self.flags is not None:
+                self.seq = (self.seq + 1) & 0xFFFFFFFF
+                check(lib.smoe_stream_write_value(self.counter.data_ptr(), self.seq, stream), "stream_write_value")
             for k in range(1, W + 1):  # right-hand neighbour first: no two ranks copy to the same destination at once
                 d = (self.rank + k) % W
                 check(lib.smoe_peer_copy(buf.ptrs[d] + dst_offsets[d] * H * item, src.data_ptr() + starts[d] * H * item,
                                          seg_rows[d] * H * item, stream), "peer_copy")
-            dist.all_reduce(self.flag, group=self.barrier_group)
+                if self.flags is not None:  # the segment has landed: tell its receiver
+                    check(lib.smoe_peer_copy(self.flags.ptrs[d] + 4 * self.rank, self.counter.data_ptr(), 4, stream),
+                          "peer_copy")
+            if self.flags is not None:
+                done = _Arrived(self.seq)
+            else:
+                dist.all_reduce(self.flag, group=self.barrier_group)
+                done = torch.cuda.Event()
+                done.record(self.comm)
             if timing:
                 e1.record(self.comm)
                 exchange_events.append((e0, e1))
-            done = torch.cuda.Event()
-            done.record(self.comm)
         src.record_stream(self.comm)
         return done, buf.rows(n_recv, H, src.dtype)
 

@@ -577,3 +577,27 @@ def test_peer_buffer_alloc_export_copy(smoe):
     assert torch.equal(back, src)
     assert lib.smoe_peer_free(p.value) == 0
     assert lib.smoe_peer_alloc(0, ctypes.byref(p)) == -1
+
+
+def test_stream_flag_write_then_wait(smoe):
+    """The arrival flags of the peer transport on one GPU: a stream writes a counter, a second stream waits until
+    the flag words have reached a value that is already (or about to be) there, then copies them out.  (Only waits
+    that will be satisfied are issued.)"""
+    _lib, _ = smoe
+    lib = _lib.lib
+    flags = torch.zeros(4, dtype=torch.int32, device="cuda")
+    counter = torch.zeros(1, dtype=torch.int32, device="cuda")
+    torch.cuda.synchronize()
+    producer, consumer = torch.cuda.Stream(), torch.cuda.Stream()
+    for seq in (1, 2, 7):
+        assert lib.smoe_stream_write_value(counter.data_ptr(), seq, producer.cuda_stream) == 0
+        for w in range(4):  # the sender's copy engine delivers its counter to each receiver word
+            assert lib.smoe_peer_copy(flags.data_ptr() + 4 * w, counter.data_ptr(), 4, producer.cuda_stream) == 0
+        assert lib.smoe_stream_wait_values(flags.data_ptr(), 4, seq, consumer.cuda_stream) == 0
+        with torch.cuda.stream(consumer):
+            seen = flags.clone()
+        consumer.synchronize()
+        assert (seen >= seq).all()
+    assert lib.smoe_stream_wait_values(flags.data_ptr(), 0, 99, consumer.cuda_stream) == 0
+    assert lib.smoe_stream_write_value(None, 1, consumer.cuda_stream) != 0
+    torch.cuda.synchronize()
