@@ -15,6 +15,18 @@ only after the kernels that read the buffer.  The buffer that receives the dispa
 holds them for the backward pass (they are the layer's saved activation), so it rotates over `depth` slots: that
 many forward passes may be in flight before their backward passes.
 
+Exchanges that run on the copy stream beside the GEMMs (`AsyncPeerTransport.send_async`) end with arrival flags
+instead of that barrier: after a destination's segment the sender copies its exchange counter into the destination's
+flag word, and whoever reads the rows makes its stream wait (a stream memory operation, no kernel) until all W
+words have reached the exchange's number.  A reader therefore waits for every sender of every exchange, and buffer
+reuse stays ordered without a global barrier.  Per buffer, written in exchange X of step n and again in step n + 1:
+a sender produces the rows of the second write only after its compute stream has consumed a later exchange Y from
+the buffer's owner, and the owner started Y after the kernels that read the buffer on its own compute stream --
+return_fwd (read by the forward pass's final sum; Y = the next step's dispatch), dispatch_bwd (read by dH and dW2;
+Y = the next step's forward return), return_bwd (read by the backward pass's final sum; Y = the next step's dispatch
+of the output gradient).  The buffer of the forward dispatch is read as late as dW1, after the dx return has already
+left, which is why it alternates between `depth` >= 2 slots (Y = any exchange of the step in between).
+
 Requirements: one process per GPU on one node, every rank able to map every other rank's memory (peer access),
 bf16 rows whose length is a multiple of 8.
 """
@@ -221,11 +233,12 @@ class _Arrived:
 
 
 class AsyncPeerTransport(PeerTransport):
-    """The peer transport with its copies on a second, high-priority stream: `send_async` returns at once with an
-    event; whoever reads the received rows makes its stream wait for that event first.  Segments travel with
-    copy-engine copies only (no kernel), so they run beside kernels that occupy every multiprocessor.  The barrier
-    after each exchange is a one-element all-reduce on a process group of its own, so that it never queues behind
-    the layer's small all-to-alls."""
+    """The peer transport with its copies on a second, high-priority stream: `send_async` returns at once with a
+    token; whoever reads the received rows hands it to `compute_wait` first.  Segments travel with copy-engine
+    copies only (no kernel), so they run beside kernels that occupy every multiprocessor, and arrival is signalled
+    by flag words that the streams write and wait for themselves.  Where the driver offers no stream memory
+    operations, each exchange ends with a one-element all-reduce on a process group of its own instead (so that it
+    never queues behind the layer's small all-to-alls)."""
 
     def __init__(self, group, device: torch.device, depth: int = 2):
         super().__init__(group, device, depth)
