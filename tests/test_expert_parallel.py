@@ -14,7 +14,7 @@ from conftest import PKG, ROOT
 from oracle import moe_oracle as orc
 
 E, K, H, I = 8, 2, 64, 64
-TOKENS = (40, 56, 24, 48)  # tokens per rank (ragged on purpose)
+TOKENS = (40, 56, 24, 48, 32, 8, 64, 16)  # tokens per rank (ragged on purpose)
 
 
 class OracleOps:
@@ -284,7 +284,7 @@ def test_expert_parallel_rank_without_rows_gloo(built_library):
     assert (res[1]["grads"][1] == 0).all() and (res[1]["grads"][2] == 0).all()
 
 
-@pytest.mark.parametrize("world,micro_batches", [(2, 1), (4, 1), (2, 2), (4, 3)])
+@pytest.mark.parametrize("world,micro_batches", [(2, 1), (4, 1), (2, 2), (4, 3), (8, 2)])
 def test_peer_transport_addressing_gloo(built_library, world, micro_batches):
     """Segments written at the plan's offsets into the other ranks' buffers reproduce the all-to-all's result, also
     with the tokens cut into chunks that are exchanged and computed one after the other."""
