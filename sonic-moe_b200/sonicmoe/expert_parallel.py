@@ -247,8 +247,6 @@ class Fp8CudaOps(CudaOps):
     """As CudaOps, with the local experts' forward and activation-gradient GEMMs in FP8 (E4M3, block scales;
     ``scale_format`` "fp32", "ue8m0" or None for the FP8 module's default)."""
 
-    shares_weight_grads = False
-
     def __init__(self, scale_format: str | None = None):
         self.scale_format = scale_format
 
@@ -258,6 +256,7 @@ class Fp8CudaOps(CudaOps):
 
         R = x_rows.shape[0]
         route = self._route(tokens, experts, num_local_experts, R)
+        route.on_dx, route.wgrad_sum = on_dx, wgrad_sum
         return _RoutedExpertsFp8.apply(x_rows, w1.permute(1, 2, 0), w2.permute(1, 2, 0), scores, route, R, inference,
                                        self.scale_format)
 

@@ -215,14 +215,8 @@ class _RoutedExpertsFp8(torch.autograd.Function):
             ds = torch.empty_like(scores_flat)
             check(lib.smoe_ds_reduce(ds_partial.data_ptr(), route.s_scatter_idx.data_ptr(), ds.data_ptr(),
                                      _lib.dtype_code(ds.dtype), TK, ncols, stream), "ds_reduce")
-            dw2 = torch.empty_like(w2e)
-            check(lib.smoe_down_projection_weight_grad(
-                dout.data_ptr(), y1s.data_ptr(), dw2.data_ptr(), off, gat, T, H, I, E, TK, st.status.data_ptr(),
-                stream), "down_projection_weight_grad")
-            dw1 = torch.empty_like(w1e)
-            check(lib.smoe_up_projection_weight_grad(
-                x.data_ptr(), dz.data_ptr(), dw1.data_ptr(), off, gat, T, H, I, E, TK, st.status.data_ptr(), stream),
-                "up_projection_weight_grad")
+            # dX before the weight gradients (bf16 GEMMs): nothing downstream waits for those, and an expert-parallel
+            # caller sends dx back to the tokens' ranks while they run (route.on_dx)
             if not fused_dz:
                 dzq, dzs = quantize_rows(dz, fmt)
             dx = torch.empty(T, H, dtype=x.dtype, device=dev)
@@ -239,6 +233,24 @@ class _RoutedExpertsFp8(torch.autograd.Function):
                     dx_expanded.data_ptr(), dx.data_ptr(), None, _lib.SMOE_F32,
                     route.s_reverse_scatter_idx.data_ptr(), ptr(route.token_offset), T, H, max(route.K, 1), stream),
                     "gather_sum")
+                del dx_expanded
+            if route.on_dx is not None:
+                route.on_dx(dx)
+            shared = route.wgrad_sum
+            if shared is None:
+                dw1, dw2, add = torch.empty_like(w1e), torch.empty_like(w2e), False
+            else:
+                dw1, dw2, add = shared.buffers(w1e, w2e)
+            down = lib.smoe_down_projection_weight_grad_accumulate if add else lib.smoe_down_projection_weight_grad
+            check(down(dout.data_ptr(), y1s.data_ptr(), dw2.data_ptr(), off, gat, T, H, I, E, TK,
+                       st.status.data_ptr(), stream), "down_projection_weight_grad")
+            up = lib.smoe_up_projection_weight_grad_accumulate if add else lib.smoe_up_projection_weight_grad
+            check(up(x.data_ptr(), dz.data_ptr(), dw1.data_ptr(), off, gat, T, H, I, E, TK, st.status.data_ptr(),
+                     stream), "up_projection_weight_grad")
+            if shared is not None:
+                dw1, dw2 = shared.finish_chunk()
+                if dw1 is None:
+                    return dx, None, None, ds, None, None, None, None
         return dx, dw1.permute(1, 2, 0), dw2.permute(1, 2, 0), ds, None, None, None, None
 
 

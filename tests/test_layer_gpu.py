@@ -300,12 +300,15 @@ def test_second_device_in_one_process(built_library):
         assert torch.equal(a, b)
 
 
-def test_chunks_share_weight_gradient_buffers(built_library):
+@pytest.mark.parametrize("kind", ["bf16", "fp8"])
+def test_chunks_share_weight_gradient_buffers(built_library, kind):
     """A batch processed as three chunks that share a `WeightGradSum`: the last chunk's backward pass hands autograd
     the sum of the chunks' weight gradients (accumulated in the GEMM epilogues), the others hand it nothing; the
     parameters' gradients match the whole batch's within bf16 accumulation error, and the two-chunk case equals
-    autograd's own accumulation of per-chunk gradients bit for bit."""
+    autograd's own accumulation of per-chunk gradients bit for bit.  The `on_dx` hook sees each chunk's dx before
+    the chunk's weight gradients are launched.  Same contract for the FP8 local experts."""
     from sonicmoe import _lib, functional as fn
+    from sonicmoe.functional.fp8 import _RoutedExpertsFp8
 
     T, H, I, E, K = 1536, 512, 256, 8, 2
     g = torch.Generator(device="cuda").manual_seed(11)
@@ -313,29 +316,35 @@ def test_chunks_share_weight_gradient_buffers(built_library):
     def rn(*shape, std):
         return (torch.randn(*shape, generator=g, device="cuda") * std).bfloat16()
 
-    x, dout = rn(T, H, std=1.0), rn(T, H, std=1.0)
+    x0, dout = rn(T, H, std=1.0), rn(T, H, std=1.0)
     w1, w2 = rn(E, 2 * I, H, std=0.05).requires_grad_(True), rn(E, H, I, std=0.05).requires_grad_(True)
     logits = rn(T, E, std=1.0)
     scores, idx = fn.topk_softmax(logits, K)
 
     def run(bounds, share):
         w1.grad = w2.grad = None
+        x = x0.clone().requires_grad_(True)
         shared = fn.WeightGradSum(len(bounds) - 1) if share else None
-        outs = []
+        outs, announced = [], []
         for a, b in zip(bounds[:-1], bounds[1:]):
             route = fn._route_metadata(idx[a:b].reshape(-1), None, E, K)
             route.wgrad_sum = shared
-            outs.append(fn._RoutedExperts.apply(x[a:b], w1.permute(1, 2, 0), w2.permute(1, 2, 0),
-                                                scores[a:b].reshape(-1), route, b - a, False))
+            route.on_dx = lambda dx, a=a, b=b: announced.append((a, b, dx.clone()))
+            args = (x[a:b], w1.permute(1, 2, 0), w2.permute(1, 2, 0), scores[a:b].reshape(-1), route, b - a, False)
+            outs.append(_RoutedExpertsFp8.apply(*args, "ue8m0") if kind == "fp8" else fn._RoutedExperts.apply(*args))
         torch.cat(outs).backward(dout)
         torch.cuda.synchronize()
         _lib.check_status()
+        assert len(announced) == len(bounds) - 1
+        for a, b, dx in announced:
+            assert torch.equal(dx, x.grad[a:b])
         return w1.grad.clone(), w2.grad.clone()
 
     whole = run([0, T], False)
+    tol = 1e-2  # FP8 too: activations are quantised row by row, so cutting the batch changes no quantised value
     for bounds in ([0, 700, T], [0, 100, 100, T]):  # uneven chunks; an empty one
         separate, shared = run(bounds, False), run(bounds, True)
         for a, b, c in zip(shared, separate, whole):
-            assert rel(a, c) < 1e-2 and rel(b, c) < 1e-2
+            assert rel(a, c) < tol and rel(b, c) < tol
             if len(bounds) == 3:
                 assert torch.equal(a, b)
