@@ -321,8 +321,9 @@ int smoe_up_projection_backward_dx(const void* dz, const void* w1, void* dx_expa
 int smoe_up_projection_backward_dx_rows(const void* dz, const void* w1, void* dx, const int* expert_offset,
                                         const int* x_gather_idx, int H, int I, int E, int TK, int* status,
                                         void* stream) {
-  if (bad_shape(H, I, E) || TK < 0 || x_gather_idx == nullptr) return SMOE_ERR_SHAPE;
+  if (bad_shape(H, I, E) || TK < 0) return SMOE_ERR_SHAPE;
   if (TK == 0) return SMOE_OK;
+  if (x_gather_idx == nullptr) return SMOE_ERR_SHAPE;
   CUtensorMap tmA, tmB;
   SMOE_TRY(encode_2d(&tmA, dz, TK, 2 * I, 2 * I, BM, BK));
   SMOE_TRY(encode_2d(&tmB, w1, (uint64_t)E * 2 * I, H, H, BK, 64));    // W1[e] (2I, H): rows are k, MN-major

@@ -386,8 +386,9 @@ int smoe_mxfp8_up_projection_forward_q(const void* xq, const void* x_scale, cons
                                        void* z, void* y1q, void* y1_scale, const int* expert_offset,
                                        const int* x_gather_idx, int T, int H, int I, int E, int TK, int* status,
                                        void* stream) {
-  if (bad_shape(H, I, E) || bad_tokens(T, TK) || y1q == nullptr || y1_scale == nullptr) return SMOE_ERR_SHAPE;
-  if (TK == 0) return SMOE_OK;
+  if (bad_shape(H, I, E) || bad_tokens(T, TK)) return SMOE_ERR_SHAPE;
+  if (TK == 0) return SMOE_OK;  // nothing to write: the (empty) output buffers may be null
+  if (y1q == nullptr || y1_scale == nullptr) return SMOE_ERR_SHAPE;
   CUtensorMap tmA, tmB;
   SMOE_TRY(encode_u8(&tmA, xq, T, H, 1, BK));
   SMOE_TRY(encode_u8(&tmB, w1q, (uint64_t)E * 2 * I, H, BN_CTA, BK));
@@ -444,8 +445,9 @@ int smoe_mxfp8_up_projection_backward_dx_rows(const void* dzq, const void* dz_sc
                                               const void* w1_scale, void* dx, const int* expert_offset,
                                               const int* x_gather_idx, int H, int I, int E, int TK, int* status,
                                               void* stream) {
-  if (bad_shape(H, I, E) || TK < 0 || x_gather_idx == nullptr) return SMOE_ERR_SHAPE;
+  if (bad_shape(H, I, E) || TK < 0) return SMOE_ERR_SHAPE;
   if (TK == 0) return SMOE_OK;
+  if (x_gather_idx == nullptr) return SMOE_ERR_SHAPE;
   CUtensorMap tmA, tmB;
   SMOE_TRY(encode_u8(&tmA, dzq, TK, 2 * I, BM, BK));
   SMOE_TRY(encode_u8(&tmB, w1q, (uint64_t)E * 2 * I, H, BK, BN_CTA));  // W1[e] (2I, H): rows are k
@@ -499,7 +501,7 @@ int smoe_mxfp8_down_projection_backward_act_q(const void* doutq, const void* dou
                                               void* dz_scale, const int* expert_offset, const int* x_gather_idx,
                                               const int* s_scatter_idx, int T, int H, int I, int E, int TK,
                                               int* status, void* stream) {
-  if (dzq == nullptr || dz_scale == nullptr) return SMOE_ERR_SHAPE;
+  if (TK > 0 && (dzq == nullptr || dz_scale == nullptr)) return SMOE_ERR_SHAPE;
   return mxfp8_dh(dzq, dz_scale, doutq, dout_scale, w2q, w2_scale, z, scores, scores_are_bf16, dz, y1s, ds_partial,
                   expert_offset, x_gather_idx, s_scatter_idx, T, H, I, E, TK, status, stream);
 }
