@@ -646,9 +646,6 @@ def close_default_transports() -> None:
     _default_transports.clear()
 
 
-MIN_TOKENS_PER_MICRO_BATCH = 1024
-
-
 def moe_ep_softmax_topk_layer(x, router_w, w1_local, w2_local, K, num_experts, group=None, ops=None,
                               is_inference_mode_enabled=False, logit_bias=None, transport=None):
     """Expert-parallel token-choice top-K layer.
