@@ -147,3 +147,25 @@ def test_fp8_layer_refuses_biases_and_other_activations(built_library):
         moe_fp8_softmax_topk_layer(inp["x"], m.router.weight, w1, b1, w2, b2, 2)
     with pytest.raises(NotImplementedError):
         moe_fp8_softmax_topk_layer(inp["x"], m.router.weight, w1, None, w2, None, 2, 0, "geglu")
+
+
+def test_weight_grad_sum_bookkeeping():
+    """`WeightGradSum`: the first chunk gets fresh buffers and stores, later chunks get the same buffers and add, only
+    the last chunk hands the gradients on, and the object is empty again afterwards."""
+    import torch
+
+    from sonicmoe.functional import WeightGradSum
+
+    w1, w2 = torch.zeros(2, 4, 3), torch.zeros(2, 3, 2)
+    shared = WeightGradSum(3)
+    d1, d2, add = shared.buffers(w1, w2)
+    assert not add and d1.shape == w1.shape and d2.shape == w2.shape
+    assert shared.finish_chunk() == (None, None)
+    e1, e2, add = shared.buffers(w1, w2)
+    assert add and e1 is d1 and e2 is d2
+    assert shared.finish_chunk() == (None, None)
+    f1, f2, add = shared.buffers(w1, w2)
+    assert add and f1 is d1
+    out1, out2 = shared.finish_chunk()
+    assert out1 is d1 and out2 is d2
+    assert shared.dw1 is None and shared.dw2 is None and shared.remaining == 0
