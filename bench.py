@@ -836,6 +836,38 @@ def run_ep_arm(args, rank, world, local_rank, workload):
     e2e_ms = timed(lambda: steps_e2e(args.steps), 1) / args.steps
     _lib.check_status(dev)
 
+    # The four row exchanges of a step alone (no GEMMs between them, ranks aligned by a barrier): what the transfers
+    # cost at the link, apart from the waiting for slower ranks that the per-exchange times of a real step include.
+    exchange_alone = None
+    transport = ep.default_transport(None, x, ops or ep.CudaOps()) if world > 1 else None
+    if transport is not None and hasattr(transport, "impl"):
+        with torch.no_grad():
+            logits_ = torch.nn.functional.linear(x.detach(), router_w.detach())
+            if logit_bias is not None:
+                logits_ = logits_ + logit_bias.to(logits_.dtype)
+            _, idx_ = (ops or ep.CudaOps()).topk_softmax(logits_, K)
+            plan = ep.plan_dispatch(idx_, E, world, None)[0]
+            impl = transport.impl
+
+            def exchanges():
+                rows = impl.dispatch_rows(x.detach(), plan, ("bench_dispatch",))
+                impl.return_rows(rows, plan, ("bench_return",))
+                rows = impl.dispatch_rows(dout, plan, ("bench_dispatch",))
+                impl.return_rows(rows, plan, ("bench_return",))
+
+            exchanges()
+            alone_ms = timed(exchanges, args.steps)
+        out_rows = sum(r for d, r in enumerate(plan.send_rows) if d != rank)   # dispatches
+        back_rows = sum(r for s_, r in enumerate(plan.recv_rows) if s_ != rank)  # returns
+        sent_t = torch.tensor([2.0 * (out_rows + back_rows) * H * 2], device=dev)
+        dist.all_reduce(sent_t, op=dist.ReduceOp.MAX)
+        exchange_alone = {"ms_per_step": alone_ms, "share_of_step": alone_ms / ms_per_step,
+                          "bytes_to_other_ranks_per_step": sent_t.item(),
+                          "gbs_per_direction": sent_t.item() / (alone_ms * 1e-3) / 1e9,
+                          "note": "dispatch x, return, dispatch dout, return, back to back with their barriers; "
+                                  "GB/s = bytes one rank sends to other ranks in the four exchanges / that time "
+                                  "(measured peer copy in one direction: 770 GB/s)"}
+
     freq = stats["freq"].float()
     dist.all_reduce(freq)  # rows per expert over all ranks
     kernels = dominant = None
@@ -876,6 +908,7 @@ def run_ep_arm(args, rank, world, local_rank, workload):
             "all_to_all_note": "sum of the exchanges' durations on the streams they run on (CUDA events, max over ranks); "
                                "with the peer transport the backward return of the row gradients runs on the copy stream "
                                "beside the weight-gradient GEMMs, so part of this time is not exposed",
+            "exchanges_alone": exchange_alone,
             "expert_load_max_over_mean": (freq.max() / freq.mean()).item(),
             "rank_load_max_over_mean": (per_rank_rows.max() / per_rank_rows.mean()).item(),
             "ep_parity": parity,
